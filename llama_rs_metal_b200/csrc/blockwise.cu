@@ -2,6 +2,7 @@
 //
 // blockwise_linear: the input row is cut into B blocks, and block b is multiplied by a matrix of
 // its own:  out[t, b, :] = (W[b] x[t, b, :] + bias[b, :]) * row_scale[t, b]   with W [B, n, m]
+// (row_scale one number per token and block, or, with scale_cols = n, one per output: [T, B, n])
 // stored [out, in] per block. Rows and blocks of x and of out are addressed by strides (in
 // elements), so a block may be a part of a wider head and the result may land beside other
 // columns. Gates of a recurrence computed per block of channels, and the per-head matrices of
@@ -24,7 +25,8 @@ constexpr int kMmaDepth = 32, kMmaStride = kMmaDepth + 8;
 template <typename O>
 __global__ __launch_bounds__(kThreads) void blockwise_linear_mma_kernel(
     const __nv_bfloat16* __restrict__ x, long long x_row, long long x_block, const __nv_bfloat16* __restrict__ w,
-    const float* __restrict__ bias, const float* __restrict__ row_scale, O* __restrict__ out, long long out_row,
+    const float* __restrict__ bias, const float* __restrict__ row_scale, int scale_cols, O* __restrict__ out,
+    long long out_row,
     long long out_block, int T, int B, int n, int m) {
   __shared__ __align__(16) __nv_bfloat16 xs[2][kTile * kMmaStride];
   __shared__ __align__(16) __nv_bfloat16 ws[2][kTile * kMmaStride];
@@ -82,7 +84,7 @@ __global__ __launch_bounds__(kThreads) void blockwise_linear_mma_kernel(
   for (int half = 0; half < 2; ++half) {
     const int row = t0 + 16 * warp + g + 8 * half;
     if (row >= T) continue;
-    const float scale = row_scale != nullptr ? row_scale[static_cast<size_t>(row) * B + b] : 1.0f;
+    const float* scales = row_scale != nullptr ? row_scale + (static_cast<size_t>(row) * B + b) * scale_cols : nullptr;
     O* dst = out + static_cast<size_t>(row) * out_row + static_cast<size_t>(b) * out_block;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -92,7 +94,7 @@ __global__ __launch_bounds__(kThreads) void blockwise_linear_mma_kernel(
         if (c >= n) continue;
         float v = acc[j][2 * half + e];
         if (bias != nullptr) v += bias[static_cast<size_t>(b) * n + c];
-        if (row_scale != nullptr) v *= scale;
+        if (scales != nullptr) v *= scales[scale_cols > 1 ? c : 0];
         dst[c] = from_f32<O>(v);
       }
     }
@@ -104,7 +106,8 @@ constexpr int kRows = 32, kCols = 64, kDepth = 32;  // tile: 32 tokens x 64 outp
 template <typename X, typename WT, typename O>
 __global__ __launch_bounds__(256) void blockwise_linear_kernel(
     const X* __restrict__ x, long long x_row, long long x_block, const WT* __restrict__ w,
-    const float* __restrict__ bias, const float* __restrict__ row_scale, O* __restrict__ out, long long out_row,
+    const float* __restrict__ bias, const float* __restrict__ row_scale, int scale_cols, O* __restrict__ out,
+    long long out_row,
     long long out_block, int T, int B, int n, int m) {
   __shared__ float xs[kRows][kDepth + 1];
   __shared__ float ws[kDepth][kCols + 1];
@@ -142,14 +145,14 @@ __global__ __launch_bounds__(256) void blockwise_linear_kernel(
   for (int r = 0; r < 2; ++r) {
     const int t = t0 + 2 * ty + r;
     if (t >= T) continue;
-    const float scale = row_scale != nullptr ? row_scale[static_cast<size_t>(t) * B + b] : 1.0f;
+    const float* scales = row_scale != nullptr ? row_scale + (static_cast<size_t>(t) * B + b) * scale_cols : nullptr;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = n0 + 4 * tx + j;
       if (c >= n) continue;
       float v = acc[r][j];
       if (bias != nullptr) v += bias[static_cast<size_t>(b) * n + c];
-      if (row_scale != nullptr) v *= scale;
+      if (scales != nullptr) v *= scales[scale_cols > 1 ? c : 0];
       out[static_cast<size_t>(t) * out_row + static_cast<size_t>(b) * out_block + c] = from_f32<O>(v);
     }
   }
@@ -182,11 +185,13 @@ __global__ void rope_heads_kernel(const A* __restrict__ src, long long src_row, 
 // x_dtype / w_dtype / out_dtype: the activation's, the matrices' and the result's types; the
 // supported combinations are all-float32, and bfloat16 x and w with a bfloat16 or float32 result.
 LRM_API int lrm_blockwise_linear(const void* x, int x_dtype, long long x_row, long long x_block, const void* w,
-                                 int w_dtype, const float* bias, const float* row_scale, void* out, int out_dtype,
+                                 int w_dtype, const float* bias, const float* row_scale, int scale_cols, void* out,
+                                 int out_dtype,
                                  long long out_row, long long out_block, int tokens, int blocks, int n, int m,
                                  cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (blocks <= 0 || n <= 0 || m <= 0 || x == nullptr || w == nullptr || out == nullptr) return LRM_BAD_ARGUMENT;
+  if (row_scale != nullptr && scale_cols != 1 && scale_cols != n) return LRM_BAD_ARGUMENT;
   const int row_tiles = (tokens + kRows - 1) / kRows;
   if (blocks > 65535 || row_tiles > 65535) return LRM_UNSUPPORTED;
   auto aligned = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
@@ -196,13 +201,13 @@ LRM_API int lrm_blockwise_linear(const void* x, int x_dtype, long long x_row, lo
     if (out_dtype == LRM_BF16) {
       LRM_LAUNCH(blockwise_linear_mma_kernel<__nv_bfloat16>, mma_grid, kThreads, 0, stream,
                  static_cast<const __nv_bfloat16*>(x), x_row, x_block, static_cast<const __nv_bfloat16*>(w), bias,
-                 row_scale, static_cast<__nv_bfloat16*>(out), out_row, out_block, tokens, blocks, n, m);
+                 row_scale, scale_cols, static_cast<__nv_bfloat16*>(out), out_row, out_block, tokens, blocks, n, m);
       return 0;
     }
     if (out_dtype == LRM_F32) {
       LRM_LAUNCH(blockwise_linear_mma_kernel<float>, mma_grid, kThreads, 0, stream,
                  static_cast<const __nv_bfloat16*>(x), x_row, x_block, static_cast<const __nv_bfloat16*>(w), bias,
-                 row_scale, static_cast<float*>(out), out_row, out_block, tokens, blocks, n, m);
+                 row_scale, scale_cols, static_cast<float*>(out), out_row, out_block, tokens, blocks, n, m);
       return 0;
     }
   }
@@ -210,7 +215,8 @@ LRM_API int lrm_blockwise_linear(const void* x, int x_dtype, long long x_row, lo
 #define LRM_BLOCKWISE(XT, WT, OT)                                                                               \
   do {                                                                                                          \
     LRM_LAUNCH((blockwise_linear_kernel<XT, WT, OT>), grid, 256, 0, stream, static_cast<const XT*>(x), x_row,  \
-               x_block, static_cast<const WT*>(w), bias, row_scale, static_cast<OT*>(out), out_row, out_block,  \
+               x_block, static_cast<const WT*>(w), bias, row_scale, scale_cols, static_cast<OT*>(out), out_row,  \
+               out_block,                                                                                       \
                tokens, blocks, n, m);                                                                           \
     return 0;                                                                                                   \
   } while (0)

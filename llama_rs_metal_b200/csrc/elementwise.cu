@@ -62,6 +62,30 @@ __global__ void clamped_gate_mul8_kernel(const float* __restrict__ gate_up, __nv
   reinterpret_cast<uint4*>(out)[idx] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
 }
 
+// out = max(x, 0)^2, the activation of a feed-forward without a gate; the input may be float32 (a
+// product that keeps its sums until the activation) while the output has the activation type.
+template <typename S, typename A>
+__global__ void relu_squared_kernel(const S* __restrict__ src, A* __restrict__ out, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx >= n) return;
+  const float v = fmaxf(to_f32(src[idx]), 0.f);
+  out[idx] = from_f32<A>(v * v);
+}
+
+// four elements per thread with 16-byte loads: float32 in, bfloat16 out
+__global__ void relu_squared4_kernel(const float4* __restrict__ src, uint2* __restrict__ out, size_t groups) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx >= groups) return;
+  const float4 x = src[idx];
+  const float a = fmaxf(x.x, 0.f), b = fmaxf(x.y, 0.f), c = fmaxf(x.z, 0.f), d = fmaxf(x.w, 0.f);
+  __nv_bfloat162 lo = __floats2bfloat162_rn(a * a, b * b), hi = __floats2bfloat162_rn(c * c, d * d);
+  out[idx] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+}
+
 template <typename D>
 __global__ void add_inplace_kernel(float* __restrict__ x, const D* __restrict__ delta, size_t n) {
   const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
@@ -129,6 +153,30 @@ LRM_API int lrm_clamped_gate_mul(const void* gate_up, int in_dtype, void* out, i
     LRM_LAUNCH((clamped_gate_mul_kernel<__nv_bfloat16, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
                static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), total, inter, block,
                limit, alpha);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}
+
+LRM_API int lrm_relu_squared(const void* src, int in_dtype, void* out, int out_dtype, long long n,
+                             cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const size_t total = static_cast<size_t>(n);
+  if (in_dtype == LRM_F32 && out_dtype == LRM_BF16 && total % 4 == 0 &&
+      reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 8 == 0) {
+    LRM_LAUNCH(relu_squared4_kernel, blocks_for(total / 4), 256, 0, stream, static_cast<const float4*>(src),
+               static_cast<uint2*>(out), total / 4);
+    return 0;
+  }
+  if (in_dtype == LRM_F32 && out_dtype == LRM_F32)
+    LRM_LAUNCH((relu_squared_kernel<float, float>), blocks_for(total), 256, 0, stream,
+               static_cast<const float*>(src), static_cast<float*>(out), total);
+  else if (in_dtype == LRM_F32 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((relu_squared_kernel<float, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const float*>(src), static_cast<__nv_bfloat16*>(out), total);
+  else if (in_dtype == LRM_BF16 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((relu_squared_kernel<__nv_bfloat16, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(out), total);
   else
     return LRM_BAD_ARGUMENT;
   return 0;

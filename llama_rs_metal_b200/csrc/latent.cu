@@ -2,12 +2,14 @@
 //
 // The projection row holds, at given columns: the query latent (q_rank columns), optionally the
 // key/value latent (kv_rank columns) followed by one key part of `rot` columns that all heads
-// share and that is rotated by position, and one gate pre-activation per head. One CTA per token:
+// share and that is rotated by position, and `gates` gate pre-activations (one per head, or one
+// per head and value dimension). One CTA per token:
 //   cq   = RMSnorm(query latent) * wq                       -> [T, q_rank], activation type
+//          (without wq: the q_rank columns as they are, for a design whose queries have no latent)
 //   row  = [RMSnorm(key/value latent) * wc | rotate(shared key part)]
 //          -> [T, kv_rank + rot] packed (a prompt attends to its own rows), and into the paged
 //             cache (one key head of width kv_rank + rot; the values are its first kv_rank columns)
-//   gate = sigmoid(gate pre-activation)                      -> [T, heads], float32
+//   gate = sigmoid(gate pre-activation)                      -> [T, gates], float32
 // Norm statistics, the rotation's angle (float(position) * inv_freq[i], pairs i, i + rot/2) and
 // the gate are float32. A layer that reads another layer's latent has no key/value columns
 // (c_off < 0) and writes no row. dest_rows[t] = page * page_size + row in page, < 0: not kept.
@@ -26,7 +28,7 @@ __global__ __launch_bounds__(256) void latent_prepare_kernel(
   pdl_wait();
   const int t = blockIdx.x;
   const S* src = proj + static_cast<size_t>(t) * stride;
-  {
+  if (wq != nullptr) {
     float ss = 0.f;
     for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
       const float v = to_f32(src[q_off + i]);
@@ -35,6 +37,9 @@ __global__ __launch_bounds__(256) void latent_prepare_kernel(
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(q_rank) + eps);
     for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
       cq_out[static_cast<size_t>(t) * q_rank + i] = from_f32<A>((to_f32(src[q_off + i]) * inv) * wq[i]);
+  } else {
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
+      cq_out[static_cast<size_t>(t) * q_rank + i] = from_f32<A>(to_f32(src[q_off + i]));
   }
   for (int h = threadIdx.x; h < heads; h += blockDim.x)
     gate_out[static_cast<size_t>(t) * heads + h] = 1.0f / (1.0f + expf(-to_f32(src[g_off + h])));
@@ -74,7 +79,7 @@ LRM_API int lrm_latent_prepare(const void* proj, int proj_dtype, long long strid
                                void* pages, const int* dest_rows, int g_off, int heads, float* gate_out,
                                int out_dtype, int tokens, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (proj == nullptr || q_rank <= 0 || wq == nullptr || cq_out == nullptr || heads <= 0 || gate_out == nullptr ||
+  if (proj == nullptr || q_rank < 0 || (q_rank > 0 && cq_out == nullptr) || heads <= 0 || gate_out == nullptr ||
       !(eps > 0.f))
     return LRM_BAD_ARGUMENT;
   if (c_off >= 0 && (kv_rank <= 0 || wc == nullptr || rot < 0 || rot % 2 ||

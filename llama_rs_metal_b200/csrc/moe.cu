@@ -4,6 +4,15 @@
 // bias; the `top` largest are chosen (the lower index wins a tie) and weighted by the softmax
 // over the chosen logits only.
 //
+// Scored router (lrm_moe_router / lrm_moe_route with `scored`): s = softmax(z) over all E outputs;
+// the choice is made on s + correction (a stored vector, may be absent) and the weights are the
+// chosen s themselves (divided by their sum with `renormalize`). The outputs form `groups` equal
+// groups of neighbours; a group's score is its largest choice score, and only outputs of the
+// `keep` best groups can be chosen (the lower index wins every tie). Outputs numbered `experts`
+// and above are identity experts: they have no matrices and return their input.
+//
+// Activation of an expert (`act`): 0, the clamped gate below; 1, silu(gate) * up.
+//
 // Experts, token by token (lrm_moe_experts_rows): one CTA per (token, chosen expert, slice of
 // the expert's inner width). It forms its slice of
 //   y = act(W_gate x, W_up x),   clamped gate:  g = min(g, limit), u = clamp(u, -limit, limit),
@@ -27,6 +36,114 @@
 #include "common.cuh"
 
 namespace {
+
+__device__ __forceinline__ float expert_activation(float g, float u, int act, float limit, float alpha) {
+  if (act == 1) return g / (1.0f + expf(-g)) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
+// A warp turns logits z [E] into s = softmax(z) and choice = s + correction (both [E], shared memory).
+__device__ __forceinline__ void score_row(const float* __restrict__ z, const float* __restrict__ correction,
+                                          float* __restrict__ s, float* __restrict__ choice, int E, int lane) {
+  float top = -INFINITY;
+  for (int e = lane; e < E; e += 32) top = fmaxf(top, z[e]);
+  for (int o = 16; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+  float mass = 0.f;
+  for (int e = lane; e < E; e += 32) mass += expf(z[e] - top);
+  mass = warp_sum(mass);
+  for (int e = lane; e < E; e += 32) {
+    const float v = expf(z[e] - top) / mass;
+    s[e] = v;
+    choice[e] = v + (correction != nullptr ? correction[e] : 0.f);
+  }
+}
+
+// One thread: the `keep` best of `groups` groups by their largest choice score, then the `top` best
+// allowed outputs; `open` [groups] is scratch. The weights are the chosen s.
+__device__ void choose_scored(const float* __restrict__ s, const float* __restrict__ choice, unsigned char* open,
+                              int E, int top, int groups, int keep, int renormalize, int* __restrict__ ids,
+                              float* __restrict__ weights) {
+  const int size = E / groups;
+  if (groups > 1 && keep < groups) {
+    for (int g = 0; g < groups; ++g) open[g] = 0;
+    for (int c = 0; c < keep; ++c) {
+      int arg = -1;
+      float val = -INFINITY;
+      for (int g = 0; g < groups; ++g) {
+        if (open[g]) continue;
+        float best = -INFINITY;
+        for (int e = g * size; e < (g + 1) * size; ++e) best = fmaxf(best, choice[e]);
+        if (arg < 0 || best > val) {
+          arg = g;
+          val = best;
+        }
+      }
+      open[arg] = 1;
+    }
+  } else {
+    for (int g = 0; g < groups; ++g) open[g] = 1;
+  }
+  float mass = 0.f;
+  for (int c = 0; c < top; ++c) {
+    int arg = -1;
+    float val = -INFINITY;
+    for (int e = 0; e < E; ++e) {
+      if (!open[e / size]) continue;
+      bool taken = false;
+      for (int p = 0; p < c; ++p) taken |= ids[p] == e;
+      if (!taken && (arg < 0 || choice[e] > val)) {
+        arg = e;
+        val = choice[e];
+      }
+    }
+    ids[c] = arg;
+    weights[c] = s[arg];
+    mass += s[arg];
+  }
+  if (renormalize)
+    for (int c = 0; c < top; ++c) weights[c] /= mass;
+}
+
+// Scored routing from logits [T, E]: one warp per token; shared memory per warp: s [E], choice [E],
+// and the groups' flags.
+__global__ void moe_route_scored_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
+                                        int* __restrict__ ids, float* __restrict__ weights, int tokens, int E,
+                                        int top, int groups, int keep, int renormalize) {
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int t = blockIdx.x * warps + warp;
+  if (t >= tokens) return;
+  const int per = 2 * E + (groups + 3) / 4;
+  float* s = smem + static_cast<size_t>(warp) * per;
+  float* choice = s + E;
+  score_row(logits + static_cast<size_t>(t) * E, correction, s, choice, E, lane);
+  __syncwarp();
+  if (lane == 0)
+    choose_scored(s, choice, reinterpret_cast<unsigned char*>(choice + E), E, top, groups, keep, renormalize,
+                  ids + static_cast<size_t>(t) * top, weights + static_cast<size_t>(t) * top);
+}
+
+// out[t, :] += (sum of the weights of the identity experts token t chose) * x[t, :]; x is the
+// float32 input itself where the caller has it, else its rounding.
+template <typename A>
+__global__ void moe_identity_add_kernel(float* __restrict__ out, const A* __restrict__ x, const int* __restrict__ ids,
+                                        const float* __restrict__ weights, int width, int experts, int top) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  float w = 0.f;
+  for (int c = 0; c < top; ++c)
+    if (ids[static_cast<size_t>(t) * top + c] >= experts) w += weights[static_cast<size_t>(t) * top + c];
+  if (w == 0.f) return;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const size_t at = static_cast<size_t>(t) * width + i;
+    out[at] = fmaf(w, to_f32(x[at]), out[at]);
+  }
+}
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, const float* __restrict__ bias,
                                  int* __restrict__ ids, float* __restrict__ weights, int tokens, int E,
@@ -70,10 +187,11 @@ template <typename A>
 __global__ void moe_router_kernel(const A* __restrict__ x, const float* __restrict__ w,
                                   const float* __restrict__ bias, int* __restrict__ ids,
                                   float* __restrict__ weights, float* __restrict__ logits, int width, int E,
-                                  int top) {
+                                  int top, int scored, const float* __restrict__ correction, int groups, int keep,
+                                  int renormalize) {
   extern __shared__ float smem[];
   float* xs = smem;          // [width]
-  float* zs = smem + width;  // [E]
+  float* zs = smem + width;  // [E] (scored: also s [E], choice [E] and the groups' flags behind it)
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -89,9 +207,18 @@ __global__ void moe_router_kernel(const A* __restrict__ x, const float* __restri
   __syncthreads();
   if (logits != nullptr)
     for (int e = threadIdx.x; e < E; e += blockDim.x) logits[static_cast<size_t>(t) * E + e] = zs[e];
-  if (threadIdx.x != 0) return;
   int* mine = ids + static_cast<size_t>(t) * top;
   float* out = weights + static_cast<size_t>(t) * top;
+  if (scored) {
+    if (warp != 0) return;
+    score_row(zs, correction, zs + E, zs + 2 * E, E, lane);
+    __syncwarp();
+    if (lane == 0)
+      choose_scored(zs + E, zs + 2 * E, reinterpret_cast<unsigned char*>(zs + 3 * E), E, top, groups, keep,
+                    renormalize, mine, out);
+    return;
+  }
+  if (threadIdx.x != 0) return;
   float best = -INFINITY, mass = 0.f;
   for (int c = 0; c < top; ++c) {
     int arg = -1;
@@ -206,7 +333,8 @@ template <typename A, typename W>
 __global__ __launch_bounds__(256) void moe_experts_rows_kernel(
     const A* __restrict__ x, const W* __restrict__ gate_up, const W* __restrict__ down,
     const int* __restrict__ ids, const float* __restrict__ weights, float* __restrict__ planes, int tokens,
-    int width, int ff, int experts, int top, int slices, float limit, float alpha) {
+    int width, int ff, int experts, int top, int slices, float limit, float alpha, int act,
+    const float* __restrict__ x32) {
   extern __shared__ float smem[];
   float* xs = smem;          // [width]
   float* ys = smem + width;  // [slice length]
@@ -216,6 +344,14 @@ __global__ __launch_bounds__(256) void moe_experts_rows_kernel(
   pdl_wait();
   const int e = ids[static_cast<size_t>(t) * top + c];
   const float weight = weights[static_cast<size_t>(t) * top + c];
+  if (e >= experts) {  // an identity expert: its output is its input, counted once (by slice 0)
+    float* dst = planes + (static_cast<size_t>(c) * slices + s) * tokens * width + static_cast<size_t>(t) * width;
+    for (int r = threadIdx.x; r < width; r += blockDim.x) {
+      const size_t at = static_cast<size_t>(t) * width + r;
+      dst[r] = s == 0 ? weight * (x32 != nullptr ? x32[at] : to_f32(x[at])) : 0.f;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = to_f32(x[static_cast<size_t>(t) * width + i]);
   __syncthreads();
   const W* wg = gate_up + static_cast<size_t>(e) * 2 * ff * width;
@@ -225,11 +361,7 @@ __global__ __launch_bounds__(256) void moe_experts_rows_kernel(
   for (int f = f0 + warp; f < f1; f += warps) {
     float g, u;
     row_dot2(wg + static_cast<size_t>(f) * width, wu + static_cast<size_t>(f) * width, xs, width, wide_ok, lane, &g, &u);
-    if (lane == 0) {
-      g = fminf(g, limit);
-      u = fminf(fmaxf(u, -limit), limit);
-      ys[f - f0] = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
-    }
+    if (lane == 0) ys[f - f0] = expert_activation(g, u, act, limit, alpha);
   }
   __syncthreads();
   // the slice's share of the down projection: a thread per output, the slice's columns in order
@@ -258,7 +390,7 @@ __global__ __launch_bounds__(256) void moe_experts_rows_kernel(
 template <typename G, typename A>
 __global__ void moe_dense_gate_kernel(const G* __restrict__ gu, const int* __restrict__ ids,
                                       const float* __restrict__ weights, A* __restrict__ y, int ff,
-                                      int experts, int top, float limit, float alpha) {
+                                      int experts, int top, float limit, float alpha, int act) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -270,10 +402,8 @@ __global__ void moe_dense_gate_kernel(const G* __restrict__ gu, const int* __res
       if (ids[static_cast<size_t>(t) * top + c] == e) w = weights[static_cast<size_t>(t) * top + c];
     float out = 0.f;
     if (w != 0.f) {
-      float g = to_f32(gu[(row + e) * 2 * ff + f]), u = to_f32(gu[(row + e) * 2 * ff + ff + f]);
-      g = fminf(g, limit);
-      u = fminf(fmaxf(u, -limit), limit);
-      out = g / (1.0f + expf(-alpha * g)) * (u + 1.0f) * w;
+      const float g = to_f32(gu[(row + e) * 2 * ff + f]), u = to_f32(gu[(row + e) * 2 * ff + ff + f]);
+      out = expert_activation(g, u, act, limit, alpha) * w;
     }
     y[row * ff + item] = from_f32<A>(out);
   }
@@ -284,21 +414,21 @@ __global__ void moe_dense_gate_kernel(const G* __restrict__ gu, const int* __res
 // gu: float32 or the type of y (`gu_dtype`); y: `dtype`.
 LRM_API int lrm_moe_dense_gate(const void* gu, int gu_dtype, int dtype, const int* ids, const float* weights,
                                void* y, int tokens, int ff, int experts, int top, float limit, float alpha,
-                               cudaStream_t stream) {
+                               int act, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (ff <= 0 || experts <= 0 || top <= 0 || top > experts) return LRM_BAD_ARGUMENT;
+  if (ff <= 0 || experts <= 0 || top <= 0 || (act != 0 && act != 1)) return LRM_BAD_ARGUMENT;
   const long long items = static_cast<long long>(experts) * ff;
   const dim3 grid(tokens, static_cast<unsigned>((items + 1023) / 1024));
   if (dtype == LRM_BF16 && gu_dtype == LRM_BF16)
     LRM_LAUNCH((moe_dense_gate_kernel<__nv_bfloat16, __nv_bfloat16>), grid, 256, 0, stream,
                static_cast<const __nv_bfloat16*>(gu), ids, weights, static_cast<__nv_bfloat16*>(y), ff, experts, top,
-               limit, alpha);
+               limit, alpha, act);
   else if (dtype == LRM_BF16 && gu_dtype == LRM_F32)
     LRM_LAUNCH((moe_dense_gate_kernel<float, __nv_bfloat16>), grid, 256, 0, stream, static_cast<const float*>(gu),
-               ids, weights, static_cast<__nv_bfloat16*>(y), ff, experts, top, limit, alpha);
+               ids, weights, static_cast<__nv_bfloat16*>(y), ff, experts, top, limit, alpha, act);
   else if (dtype == LRM_F32 && gu_dtype == LRM_F32)
     LRM_LAUNCH((moe_dense_gate_kernel<float, float>), grid, 256, 0, stream, static_cast<const float*>(gu), ids,
-               weights, static_cast<float*>(y), ff, experts, top, limit, alpha);
+               weights, static_cast<float*>(y), ff, experts, top, limit, alpha, act);
   else
     return LRM_BAD_ARGUMENT;
   return 0;
@@ -314,20 +444,57 @@ LRM_API int lrm_moe_route(const float* logits, const float* bias, int* ids, floa
 
 // x [T, width] float32 or bfloat16 (widened to float32), w float32 [E, width], bias float32 [E] or
 // null -> ids int32 [T, top], weights float32 [T, top]; `logits` (float32 [T, E]) may be null.
+// `scored`: the scored router described at the top (correction float32 [E] or null, `groups` equal
+// groups of which `keep` stay open, `renormalize`); bias is then not used.
 LRM_API int lrm_moe_router(const void* x, int x_dtype, const float* w, const float* bias, int* ids,
-                           float* weights, float* logits, int tokens, int width, int E, int top,
-                           cudaStream_t stream) {
+                           float* weights, float* logits, int tokens, int width, int E, int top, int scored,
+                           const float* correction, int groups, int keep, int renormalize, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (width <= 0 || E <= 0 || top <= 0 || top > E) return LRM_BAD_ARGUMENT;
-  const size_t bytes = sizeof(float) * (static_cast<size_t>(width) + E);
+  if (scored && (groups <= 0 || E % groups || keep <= 0 || keep > groups || top > keep * (E / groups)))
+    return LRM_BAD_ARGUMENT;
+  const size_t bytes = sizeof(float) * (static_cast<size_t>(width) + (scored ? 3 * E + (groups + 3) / 4 : E));
   if (bytes > 48 * 1024) return LRM_UNSUPPORTED;
   const int threads = E >= 8 ? 256 : 128;
   if (x_dtype == LRM_F32)
     LRM_LAUNCH(moe_router_kernel<float>, tokens, threads, bytes, stream, static_cast<const float*>(x), w, bias, ids,
-               weights, logits, width, E, top);
+               weights, logits, width, E, top, scored, correction, groups, keep, renormalize);
   else if (x_dtype == LRM_BF16)
     LRM_LAUNCH(moe_router_kernel<__nv_bfloat16>, tokens, threads, bytes, stream,
-               static_cast<const __nv_bfloat16*>(x), w, bias, ids, weights, logits, width, E, top);
+               static_cast<const __nv_bfloat16*>(x), w, bias, ids, weights, logits, width, E, top, scored, correction,
+               groups, keep, renormalize);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}
+
+// The scored router's choice from float32 logits [T, E] -> ids int32 [T, top], weights float32 [T, top].
+LRM_API int lrm_moe_route_scored(const float* logits, const float* correction, int* ids, float* weights, int tokens,
+                                 int E, int top, int groups, int keep, int renormalize, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
+      top > keep * (E / groups))
+    return LRM_BAD_ARGUMENT;
+  const int warps = 4;
+  const size_t bytes = sizeof(float) * warps * (2 * static_cast<size_t>(E) + (groups + 3) / 4);
+  if (bytes > 48 * 1024) return LRM_UNSUPPORTED;
+  LRM_LAUNCH(moe_route_scored_kernel, (tokens + warps - 1) / warps, 32 * warps, bytes, stream, logits, correction, ids,
+             weights, tokens, E, top, groups, keep, renormalize);
+  return 0;
+}
+
+// out float32 [T, width] += (weights of the chosen ids >= experts, summed) * x [T, width].
+LRM_API int lrm_moe_identity_add(float* out, const void* x, int x_dtype, const int* ids, const float* weights,
+                                 int tokens, int width, int experts, int top, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0 || top <= 0 || experts < 0) return LRM_BAD_ARGUMENT;
+  const int threads = width >= 1024 ? 256 : 128;
+  if (x_dtype == LRM_F32)
+    LRM_LAUNCH(moe_identity_add_kernel<float>, tokens, threads, 0, stream, out, static_cast<const float*>(x), ids,
+               weights, width, experts, top);
+  else if (x_dtype == LRM_BF16)
+    LRM_LAUNCH(moe_identity_add_kernel<__nv_bfloat16>, tokens, threads, 0, stream, out,
+               static_cast<const __nv_bfloat16*>(x), ids, weights, width, experts, top);
   else
     return LRM_BAD_ARGUMENT;
   return 0;
@@ -344,13 +511,15 @@ LRM_API int lrm_moe_rows_slices(int tokens, int top, int ff) {
 }
 
 // x [T, width] (float32 or bfloat16); gate_up [E, 2 ff, width], down [width, E, ff] (float32 or
-// bfloat16); planes float32 [top * slices, T, width].
+// bfloat16); planes float32 [top * slices, T, width]. An id >= experts is an identity expert, whose
+// output is x32 [T, width] (float32, when given) or x.
 LRM_API int lrm_moe_experts_rows(const void* x, int x_dtype, const void* gate_up, const void* down,
                                  int w_dtype, const int* ids, const float* weights, float* planes, int tokens,
                                  int width, int ff, int experts, int top, int slices, float limit, float alpha,
-                                 cudaStream_t stream) {
+                                 int act, const float* x32, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (width <= 0 || ff <= 0 || top <= 0 || slices <= 0 || top > 65535 || tokens > 65535 || experts <= 0)
+  if (width <= 0 || ff <= 0 || top <= 0 || slices <= 0 || top > 65535 || tokens > 65535 || experts <= 0 ||
+      (act != 0 && act != 1))
     return LRM_BAD_ARGUMENT;
   const int per = (ff + slices - 1) / slices;
   const size_t bytes = sizeof(float) * (static_cast<size_t>(width) + per);
@@ -365,7 +534,7 @@ LRM_API int lrm_moe_experts_rows(const void* x, int x_dtype, const void* gate_up
     }                                                                                                      \
     LRM_LAUNCH((moe_experts_rows_kernel<AT, WT>), grid, 256, bytes, stream, static_cast<const AT*>(x),     \
                static_cast<const WT*>(gate_up), static_cast<const WT*>(down), ids, weights, planes, tokens, \
-               width, ff, experts, top, slices, limit, alpha);                                             \
+               width, ff, experts, top, slices, limit, alpha, act, x32);                                   \
   } while (0)
   if (x_dtype == LRM_F32 && w_dtype == LRM_F32)
     LRM_MOE_ROWS(float, float);

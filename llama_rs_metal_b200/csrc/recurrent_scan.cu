@@ -2,10 +2,12 @@
 // token updates and reads,
 //
 //   plain decay (retention):   S <- a S + k v^T                      o = S^T q
+//   decay per token:           S <- a_t S + k v^T                    o = S^T q
 //   gated delta rule:          S <- diag(g) S;  u = b (v - S^T k);   S <- S + k u^T;   o = S^T q
 //
-// with a one decay per head, g one decay per head and key channel and token, b one step size per
-// head and token. Everything here is float32: the inputs are prepared in float32 by the kernels
+// with a one decay per head (or, per token, one per head and token: state-space and matrix-memory
+// mixers, whose step size or input gate the caller has multiplied into v), g one decay per head
+// and key channel and token, b one step size per head and token. Everything here is float32: the inputs are prepared in float32 by the kernels
 // below (rotation, short convolutions, unit norms, decays), the state lives in float32 in the
 // cache's state storage, one matrix per slot and head, and is carried from step to step.
 //
@@ -40,13 +42,16 @@ __device__ __forceinline__ void scan_cp_async(float* dst, const float* src, bool
 // Thread (column j, part p) holds rows p * ROWS .. p * ROWS + ROWS - 1 of column j. A token's q, k
 // and g rows lie in shared memory as [P][ROWS + 4] (the 4 floats between the parts keep the parts'
 // 16-byte reads on different banks); tokens come in chunks of kChunk, two chunks in flight.
-template <int ROWS, bool DELTA>
+// MODE 0: one decay per head (head_decay); 1: the gated delta rule (g, beta); 2: one decay per head
+// and token (in `beta`'s place, [T, H]).
+template <int ROWS, int MODE>
 __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ g, const float* __restrict__ head_decay, const float* __restrict__ beta,
     float* __restrict__ state, float* __restrict__ out, const int* __restrict__ cu_seqlens,
     const int* __restrict__ slots, int H, int KH, int d, int dv, int P) {
   extern __shared__ __align__(16) float smem[];
+  constexpr bool DELTA = MODE == 1;
   constexpr int RS = ROWS + 4;
   const int TS = P * RS, COLS = kScanThreads / P;
   const int VS = (COLS + 3) & ~3;                       // v of a token, padded to whole 16 bytes
@@ -66,7 +71,7 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
     const int row = pidx * ROWS + i;
     S[i] = (mine != nullptr && row < d && j < dv) ? mine[static_cast<size_t>(row) * dv + j] : 0.f;
   }
-  const float a = DELTA ? 1.f : head_decay[h];
+  const float a = MODE == 0 ? head_decay[h] : 1.f;
   // 16-byte copies where every row of the inputs starts on a 16-byte boundary
   const bool wide = d % 4 == 0 && dv % 4 == 0 && COLS % 4 == 0;
   const int step = wide ? 4 : 1;
@@ -91,9 +96,10 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
       const bool in = col < dv;
       scan_cp_async(base + c * TOKEN + (DELTA ? 3 : 2) * TS + cl, v + (tok * H + h) * dv + (in ? col : 0), in, wide);
     }
-    if (DELTA)
+    if (MODE != 0)
       for (int c = tid; c < cn; c += kScanThreads)
-        scan_cp_async(base + c * TOKEN + 3 * TS + VS, beta + static_cast<size_t>(start + c0 + c) * H + h, true, false);
+        scan_cp_async(base + c * TOKEN + (DELTA ? 3 : 2) * TS + VS, beta + static_cast<size_t>(start + c0 + c) * H + h,
+                      true, false);
     asm volatile("cp.async.commit_group;\n" ::);
   };
 
@@ -113,13 +119,14 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
       const float* qc = base + c * TOKEN + pidx * RS;
       const float* kc = qc + TS;
       const float* gc = kc + TS;
+      const float at = MODE == 2 ? base[c * TOKEN + 2 * TS + VS] : a;
       float kr[ROWS];
       float r0 = 0.f, r1 = 0.f, s0 = 0.f, s1 = 0.f, kq0 = 0.f, kq1 = 0.f;
 #pragma unroll
       for (int i = 0; i < ROWS; i += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(kc + i);
         const float4 q4 = *reinterpret_cast<const float4*>(qc + i);
-        float4 g4 = make_float4(a, a, a, a);
+        float4 g4 = make_float4(at, at, at, at);
         if (DELTA) g4 = *reinterpret_cast<const float4*>(gc + i);
         kr[i] = k4.x, kr[i + 1] = k4.y, kr[i + 2] = k4.z, kr[i + 3] = k4.w;
         S[i] *= g4.x, S[i + 1] *= g4.y, S[i + 2] *= g4.z, S[i + 3] *= g4.w;
@@ -156,21 +163,22 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
   }
 }
 
-template <int ROWS, bool DELTA>
+template <int ROWS, int MODE>
 int launch_scan(const float* q, const float* k, const float* v, const float* g, const float* head_decay,
                 const float* beta, float* state, float* out, const int* cu_seqlens, const int* slots,
                 int seqs, int H, int KH, int d, int dv, int P, cudaStream_t stream) {
+  constexpr bool DELTA = MODE == 1;
   const int COLS = kScanThreads / P, TS = P * (ROWS + 4), VS = (COLS + 3) & ~3;
   const size_t bytes = sizeof(float) * 2 * kChunk * (static_cast<size_t>(DELTA ? 3 : 2) * TS + VS + 4);
   static bool raised = false;  // per instantiation
   if (bytes > 48 * 1024 && !raised) {
-    cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<ROWS, DELTA>,
+    cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<ROWS, MODE>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return static_cast<int>(e);
     raised = true;
   }
   const dim3 grid((dv + COLS - 1) / COLS, H, seqs);
-  LRM_LAUNCH((linear_scan_kernel<ROWS, DELTA>), grid, kScanThreads, bytes, stream, q, k, v, g, head_decay, beta,
+  LRM_LAUNCH((linear_scan_kernel<ROWS, MODE>), grid, kScanThreads, bytes, stream, q, k, v, g, head_decay, beta,
              state, out, cu_seqlens, slots, H, KH, d, dv, P);
   return 0;
 }
@@ -189,7 +197,7 @@ void scan_shape(int d, int* rows, int* parts) {
   *parts = P;
 }
 
-template <bool DELTA>
+template <int MODE>
 int dispatch_scan(const float* q, const float* k, const float* v, const float* g, const float* head_decay,
                   const float* beta, float* state, float* out, const int* cu_seqlens, const int* slots,
                   int seqs, int H, int KH, int d, int dv, cudaStream_t stream) {
@@ -197,7 +205,7 @@ int dispatch_scan(const float* q, const float* k, const float* v, const float* g
   scan_shape(d, &R, &P);
 #define LRM_SCAN_CASE(N)                                                                             \
   case N:                                                                                            \
-    return launch_scan<N, DELTA>(q, k, v, g, head_decay, beta, state, out, cu_seqlens, slots, seqs, H, \
+    return launch_scan<N, MODE>(q, k, v, g, head_decay, beta, state, out, cu_seqlens, slots, seqs, H, \
                                  KH, d, dv, P, stream)
   switch (R) {
     LRM_SCAN_CASE(4);
@@ -212,22 +220,32 @@ int dispatch_scan(const float* q, const float* k, const float* v, const float* g
 
 // --------------------------------------------------------------------------- read-out: norm and gate per head
 // out[t, h, :] = o / sqrt(mean(o^2) + eps) * w * act(gate[t, h, :]) * out_scale; w and gate optional.
+// A head's row of `o` has o_stride floats of which the first dv are read (o_stride > dv: the scan
+// carried more columns). w is shared by the heads (w_stride 0) or one row per head (w_stride dv).
+// With `floor` [T, H] the head is first divided by max(|o[dv]|, floor[t, h]) + den_eps: o's column dv
+// then holds the read-out of a normalizer that went through the scan as one more value column.
 template <typename A, typename G>
-__global__ void head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight,
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, int o_stride, const float* __restrict__ weight,
+                                      int w_stride, const float* __restrict__ floor, float den_eps,
                                       const G* __restrict__ gate, long long gate_stride, int gate_act,
                                       A* __restrict__ out, int H, int dv, float eps, float out_scale) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, h = blockIdx.y;
-  const float* row = o + (static_cast<size_t>(t) * H + h) * dv;
+  const float* row = o + (static_cast<size_t>(t) * H + h) * o_stride;
+  float under = 1.0f;
+  if (floor != nullptr) under = 1.0f / (fmaxf(fabsf(row[dv]), floor[static_cast<size_t>(t) * H + h]) + den_eps);
   float ss = 0.f;
-  for (int j = threadIdx.x; j < dv; j += blockDim.x) ss = fmaf(row[j], row[j], ss);
+  for (int j = threadIdx.x; j < dv; j += blockDim.x) {
+    const float v = row[j] * under;
+    ss = fmaf(v, v, ss);
+  }
   const float total = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(total / static_cast<float>(dv) + eps);
   for (int j = threadIdx.x; j < dv; j += blockDim.x) {
-    float y = row[j] * inv;
-    if (weight != nullptr) y *= weight[j];
+    float y = (row[j] * under) * inv;
+    if (weight != nullptr) y *= weight[h * w_stride + j];
     if (gate != nullptr) {
       const float z = to_f32(gate[static_cast<size_t>(t) * gate_stride + h * dv + j]);
       const float sig = 1.0f / (1.0f + expf(-z));
@@ -393,8 +411,9 @@ LRM_API int lrm_linear_state_scan_rows(int rows) {
 }
 
 // q, k float32 [T, KH, d]; v float32 [T, H, dv]; out float32 [T, H, dv]; state float32
-// [slots, H, d, dv]. Without `g`: plain decay per head (head_decay [H]); with it: the gated delta
-// rule (g [T, H, d], beta [T, H]).
+// [slots, H, d, dv]. Without `g`: plain decay per head (head_decay [H]) or, when that is null, per
+// head and token (`beta` [T, H] holds the decays); with it: the gated delta rule (g [T, H, d], beta
+// [T, H]).
 LRM_API int lrm_linear_state_scan(const float* q, const float* k, const float* v, const float* g,
                                   const float* head_decay, const float* beta, float* state, float* out,
                                   const int* cu_seqlens, const int* slots, int seqs, int H, int KH, int d,
@@ -404,24 +423,31 @@ LRM_API int lrm_linear_state_scan(const float* q, const float* k, const float* v
   if (d > 2048) return LRM_UNSUPPORTED;
   if (g != nullptr) {
     if (beta == nullptr) return LRM_BAD_ARGUMENT;
-    return dispatch_scan<true>(q, k, v, g, nullptr, beta, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
+    return dispatch_scan<1>(q, k, v, g, nullptr, beta, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
   }
-  if (head_decay == nullptr) return LRM_BAD_ARGUMENT;
-  return dispatch_scan<false>(q, k, v, nullptr, head_decay, nullptr, state, out, cu_seqlens, slots, seqs, H, KH, d,
-                              dv, stream);
+  if (head_decay == nullptr) {  // one decay per head and token, where beta would be
+    if (beta == nullptr) return LRM_BAD_ARGUMENT;
+    return dispatch_scan<2>(q, k, v, nullptr, nullptr, beta, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
+  }
+  return dispatch_scan<0>(q, k, v, nullptr, head_decay, nullptr, state, out, cu_seqlens, slots, seqs, H, KH, d,
+                          dv, stream);
 }
 
-// `gate` (type gate_dtype, may be null) is read at gate[t * gate_stride + h * dv + j].
-LRM_API int lrm_head_norm_gate(const float* o, const float* weight, const void* gate, int gate_dtype,
-                               long long gate_stride, int gate_act, void* out, int dtype, int tokens, int H,
-                               int dv, float eps, float out_scale, cudaStream_t stream) {
+// `gate` (type gate_dtype, may be null) is read at gate[t * gate_stride + h * dv + j]; o at
+// o[(t * H + h) * o_stride + j]; weight at weight[h * w_stride + j]; floor (may be null) at [t * H + h].
+LRM_API int lrm_head_norm_gate(const float* o, int o_stride, const float* weight, int w_stride, const float* floor,
+                               float den_eps, const void* gate, int gate_dtype, long long gate_stride, int gate_act,
+                               void* out, int dtype, int tokens, int H, int dv, float eps, float out_scale,
+                               cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (H <= 0 || H > 65535 || dv <= 0 || (gate != nullptr && gate_act != 1 && gate_act != 2)) return LRM_BAD_ARGUMENT;
+  if (o_stride < dv || (floor != nullptr && o_stride <= dv) || (w_stride != 0 && w_stride != dv)) return LRM_BAD_ARGUMENT;
   const int threads = dv >= 256 ? 256 : ((dv + 31) / 32) * 32;
   const dim3 grid(tokens, H);
 #define LRM_HEAD_NORM(AT, GT)                                                                              \
-  LRM_LAUNCH((head_norm_gate_kernel<AT, GT>), grid, threads, 0, stream, o, weight, static_cast<const GT*>(gate), \
-             gate_stride, gate_act, static_cast<AT*>(out), H, dv, eps, out_scale)
+  LRM_LAUNCH((head_norm_gate_kernel<AT, GT>), grid, threads, 0, stream, o, o_stride, weight, w_stride, floor,    \
+             den_eps, static_cast<const GT*>(gate), gate_stride, gate_act, static_cast<AT*>(out), H, dv, eps,     \
+             out_scale)
   if (dtype == LRM_F32 && gate_dtype == LRM_F32)
     LRM_HEAD_NORM(float, float);
   else if (dtype == LRM_F32 && gate_dtype == LRM_BF16)
@@ -454,6 +480,25 @@ LRM_API int lrm_retention_prepare(const void* proj, int dtype, long long stride,
     LRM_LAUNCH(retention_prepare_kernel<__nv_bfloat16>, grid, threads, 0, stream,
                static_cast<const __nv_bfloat16*>(proj), stride, q_off, k_off, v_off, positions, inv_freq, rotary,
                k_scale, qf, kf, vf, H, d, dv);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}
+
+// Every sequence's tail [slots, n - 1, C] becomes the last n - 1 inputs (columns conv_off .. conv_off
+// + C of `proj`) it has seen, for a caller whose own kernel made the convolution.
+LRM_API int lrm_conv_tail_update(const void* proj, int dtype, long long stride, int conv_off, int C, int n,
+                                 float* tails, const int* cu_seqlens, const int* slots, int seqs,
+                                 cudaStream_t stream) {
+  if (seqs <= 0 || n <= 1) return 0;
+  if (C <= 0 || seqs > 65535 || tails == nullptr) return LRM_BAD_ARGUMENT;
+  const dim3 tail_grid((C + 255) / 256, seqs);
+  if (dtype == LRM_F32)
+    LRM_LAUNCH(conv_tail_update_kernel<float>, tail_grid, 256, 0, stream, static_cast<const float*>(proj), stride,
+               conv_off, C, n, tails, cu_seqlens, slots);
+  else if (dtype == LRM_BF16)
+    LRM_LAUNCH(conv_tail_update_kernel<__nv_bfloat16>, tail_grid, 256, 0, stream,
+               static_cast<const __nv_bfloat16*>(proj), stride, conv_off, C, n, tails, cu_seqlens, slots);
   else
     return LRM_BAD_ARGUMENT;
   return 0;

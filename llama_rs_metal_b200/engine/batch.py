@@ -64,6 +64,10 @@ class StepContext:
     # writes the stream last in a block may fill `normed`; the next block takes it or ignores it.
     next_entry_norm: Any = None
     normed: Any = None
+    # The float32 stream [T, h] a sublayer's input is the rounding of, while a block whose sublayers
+    # read the stream itself runs one (None otherwise): a part that passes its input on unchanged
+    # (an identity expert) takes it from here.
+    stream: Any = None
 
     def take_normed(self, norm):
         """The stream's normalized activations if the block before left them for `norm`."""

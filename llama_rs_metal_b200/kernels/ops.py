@@ -8,6 +8,7 @@ A kernel that cannot take a size raises UnsupportedError with the reason.
 from __future__ import annotations
 
 import ctypes
+from dataclasses import dataclass
 from typing import Optional, Tuple
 
 import torch
@@ -147,6 +148,45 @@ def rms_norm_add_(stream: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, e
     return out
 
 
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out_dtype: torch.dtype,
+               rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """(x - mean) / sqrt(variance + eps) * weight + bias over float32 rows [T, h] (all, or those `rows`
+    names); weight and bias float32 [h]. -> [T or len(rows), h] in `out_dtype`."""
+    _check(x, "x", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    _check(bias, "bias", torch.float32, 1)
+    hidden = x.shape[1]
+    if weight.numel() != hidden or bias.numel() != hidden:
+        raise InvalidError("layer_norm: weight and bias must have one entry per column")
+    n_rows = x.shape[0]
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        n_rows = rows.numel()
+    out = _activation(n_rows, hidden, out_dtype, x.device)
+    _done(_lib().lrm_layer_norm(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _code(out_dtype), _ptr(rows), n_rows,
+                                hidden, ctypes.c_float(eps), _stream()), "layer_norm")
+    return out
+
+
+def layer_norm_add_(stream: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                    mult: float = 1.0, cast_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """stream += mult * layer_norm(y), in place (both float32 [T, h]: a norm behind a sublayer). With
+    `cast_dtype` the updated rows are also returned in that type, for a sublayer that reads the
+    stream itself."""
+    _check(stream, "stream", torch.float32, 2)
+    _check(y, "y", torch.float32, 2)
+    _check(weight, "weight", torch.float32, 1)
+    _check(bias, "bias", torch.float32, 1)
+    T, hidden = stream.shape
+    if tuple(y.shape) != (T, hidden) or weight.numel() != hidden or bias.numel() != hidden:
+        raise InvalidError("layer_norm_add_: y must match the stream, weight and bias its rows")
+    out = _activation(T, hidden, cast_dtype, stream.device) if cast_dtype is not None else None
+    _done(_lib().lrm_layer_norm_add(_ptr(stream), _ptr(y), _ptr(weight), _ptr(bias), ctypes.c_float(mult), _ptr(out),
+                                    _code(cast_dtype or torch.float32), T, hidden, ctypes.c_float(eps), _stream()),
+          "layer_norm_add_")
+    return out
+
+
 # --------------------------------------------------------------------------- matrix products
 STORE, ADD, SILU_GATE = "store", "add", "silu_gate"
 
@@ -266,6 +306,16 @@ def clamped_gate_mul(gate_up: torch.Tensor, block: int, limit: float, alpha: flo
     _done(_lib().lrm_clamped_gate_mul(_ptr(gate_up), _code(gate_up.dtype), _ptr(out), _code(out_dtype),
                                       ctypes.c_longlong(gate_up.shape[0]), inter, block, ctypes.c_float(limit),
                                       ctypes.c_float(alpha), _stream()), "clamped_gate_mul")
+    return out
+
+
+def relu_squared(x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """max(x, 0)^2 elementwise; x [T, I] float32 or the output's type."""
+    _check(x, "x", dims=2)
+    out_dtype = out_dtype or x.dtype
+    out = _activation(x.shape[0], x.shape[1], out_dtype, x.device)
+    _done(_lib().lrm_relu_squared(_ptr(x), _code(x.dtype), _ptr(out), _code(out_dtype), ctypes.c_longlong(x.numel()),
+                                  _stream()), "relu_squared")
     return out
 
 
@@ -478,9 +528,11 @@ def delta_prepare(proj: torch.Tensor, conv_off: int, b_off: int, a: torch.Tensor
 
 def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
                       cu_seqlens: torch.Tensor, slots: torch.Tensor, head_decay: Optional[torch.Tensor] = None,
-                      g: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      g: Optional[torch.Tensor] = None, beta: Optional[torch.Tensor] = None,
+                      token_decay: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Token-by-token update and read-out of a per-sequence, per-head matrix state (float32
-    [slots, H, d, dv], updated in place). With `head_decay` [H]: S <- a S + k v^T. With `g` [T,H,d]
+    [slots, H, d, dv], updated in place). With `head_decay` [H]: S <- a S + k v^T. With `token_decay`
+    [T,H]: S <- a_t S + k v^T, one decay per head and token. With `g` [T,H,d]
     and `beta` [T,H]: S <- diag(g) S, then S <- S + k (beta (v - S^T k))^T. o = S^T q after the
     update. q, k float32 [T,KH,d] (query head h reads q/k head h // (H/KH)), v float32 [T,H,dv].
     -> o float32 [T,H,dv]."""
@@ -492,9 +544,14 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
     H, dv = v.shape[1], v.shape[2]
     if k.shape != q.shape or v.shape[0] != T or tuple(state.shape[1:]) != (H, d, dv) or H % KH:
         raise InvalidError("linear_state_scan: shapes do not agree")
-    if (g is None) == (head_decay is None):
-        raise InvalidError("linear_state_scan: give either head_decay or g and beta")
-    if g is not None:
+    if (g is not None) + (head_decay is not None) + (token_decay is not None) != 1:
+        raise InvalidError("linear_state_scan: give head_decay, token_decay, or g and beta")
+    if token_decay is not None:
+        _check(token_decay, "token_decay", torch.float32, 2)
+        if tuple(token_decay.shape) != (T, H):
+            raise InvalidError("linear_state_scan: token_decay must be [T,H]")
+        beta = token_decay  # the kernel reads the decays where the delta rule's step sizes would be
+    elif g is not None:
         _check(g, "g", torch.float32, 3)
         _check(beta, "beta", torch.float32, 2)
         if tuple(g.shape) != (T, H, d) or tuple(beta.shape) != (T, H):
@@ -508,6 +565,127 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
                                        _ptr(out), _ptr(cu_seqlens), _ptr(slots), slots.numel(), H, KH, d, dv,
                                        _stream()), "linear_state_scan")
     return out
+
+
+def conv_tail_update_(proj: torch.Tensor, column: int, channels: int, taps: int, tails: torch.Tensor,
+                      cu_seqlens: torch.Tensor, slots: torch.Tensor) -> None:
+    """Every sequence's tail [slots, taps - 1, channels] becomes the last taps - 1 inputs (columns
+    column .. column + channels of proj [T, W]) its sequence has seen, after a kernel of the caller
+    made the convolution itself."""
+    if taps <= 1:
+        return
+    _check(proj, "proj", dims=2)
+    _check(tails, "tails", torch.float32, 3)
+    if column + channels > proj.shape[1] or tuple(tails.shape[1:]) != (taps - 1, channels):
+        raise InvalidError("conv_tail_update_: shapes do not agree")
+    _done(_lib().lrm_conv_tail_update(_ptr(proj), _code(proj.dtype), ctypes.c_longlong(proj.shape[1]), column,
+                                      channels, taps, _ptr(tails), _ptr(cu_seqlens), _ptr(slots), slots.numel(),
+                                      _stream()), "conv_tail_update_")
+
+
+def ssd_prepare(proj: torch.Tensor, conv_off: int, dt_off: int, dt_bias: torch.Tensor, rate: torch.Tensor,
+                taps: torch.Tensor, conv_bias: Optional[torch.Tensor], tails: Optional[torch.Tensor],
+                cu_seqlens: torch.Tensor, seq_of_token: torch.Tensor, slots: torch.Tensor, heads: int, groups: int,
+                state: int, value_dim: int):
+    """Inputs of a state-space mixer from its projection [T, W]: the heads * value_dim + 2 groups *
+    state channels at conv_off (x | B | C) pass a causal convolution (taps float32 [C, n], bias,
+    inputs before the step from `tails` [slots, n - 1, C], which is only read) and SiLU; dt =
+    softplus(dt + dt_bias) from the `heads` columns at dt_off; decay = exp(-rate dt).
+    -> q (= C), k (= B) [T,G,N], v (= dt x), x [T,H,dv], decay [T,H], all float32."""
+    _check(proj, "proj", dims=2)
+    T = proj.shape[0]
+    C = heads * value_dim + 2 * groups * state
+    for name, t in (("dt_bias", dt_bias), ("rate", rate)):
+        _check(t, name, torch.float32, 1)
+        if t.numel() != heads:
+            raise InvalidError(f"ssd_prepare: one entry of {name} per head")
+    _check(taps, "taps", torch.float32, 2)
+    n = taps.shape[1]
+    if conv_bias is not None:
+        _check(conv_bias, "conv_bias", torch.float32, 1)
+    if n > 1:
+        _check(tails, "tails", torch.float32, 3)
+    for name, t in (("cu_seqlens", cu_seqlens), ("seq_of_token", seq_of_token), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    if (taps.shape[0] != C or conv_off + C > proj.shape[1] or dt_off + heads > proj.shape[1] or heads % groups
+            or (conv_bias is not None and conv_bias.numel() != C)
+            or (n > 1 and tuple(tails.shape[1:]) != (n - 1, C))):
+        raise InvalidError("ssd_prepare: shapes do not agree")
+    dev = proj.device
+    q, k = _f32((T, groups, state), dev), _f32((T, groups, state), dev)
+    v, x, decay = _f32((T, heads, value_dim), dev), _f32((T, heads, value_dim), dev), _f32((T, heads), dev)
+    _done(_lib().lrm_ssd_prepare(_ptr(proj), _code(proj.dtype), ctypes.c_longlong(proj.shape[1]), conv_off, dt_off,
+                                 _ptr(dt_bias), _ptr(rate), _ptr(taps), _ptr(conv_bias), n,
+                                 _ptr(tails) if n > 1 else ctypes.c_void_p(0), _ptr(cu_seqlens), _ptr(seq_of_token),
+                                 _ptr(slots), _ptr(q), _ptr(k), _ptr(v), _ptr(x), _ptr(decay), T, heads, groups, state,
+                                 value_dim, _stream()), "ssd_prepare")
+    return q, k, v, x, decay
+
+
+def skip_gate_part_norm(o: torch.Tensor, x: torch.Tensor, skip: torch.Tensor, z: torch.Tensor, z_column: int,
+                        weight: torch.Tensor, parts: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """y = (o + skip_h x) * silu(z), each of `parts` equal parts of a row divided by its own root mean
+    square (eps inside the root), times weight. o, x float32 [T,H,dv]; skip float32 [H]; z: the H*dv
+    columns at z_column of an activation [T, W]; weight float32 [H*dv]. -> [T, H*dv] in out_dtype."""
+    _check(o, "o", torch.float32, 3)
+    _check(x, "x", torch.float32, 3)
+    _check(skip, "skip", torch.float32, 1)
+    _check(weight, "weight", torch.float32, 1)
+    _check(z, "z", dims=2)
+    T, H, dv = o.shape
+    inner = H * dv
+    if (x.shape != o.shape or skip.numel() != H or weight.numel() != inner or z.shape[0] != T
+            or z_column + inner > z.shape[1] or parts <= 0 or inner % parts):
+        raise InvalidError("skip_gate_part_norm: shapes do not agree")
+    out = _activation(T, inner, out_dtype, o.device)
+    _done(_lib().lrm_skip_gate_part_norm(_ptr(o), _ptr(x), _ptr(skip), _column_ptr(z, z_column), _code(z.dtype),
+                                         ctypes.c_longlong(z.shape[1]), _ptr(weight), _ptr(out), _code(out_dtype), T,
+                                         inner, dv, parts, ctypes.c_float(eps), _stream()), "skip_gate_part_norm")
+    return out
+
+
+def capped_gates(gates: torch.Tensor, i_column: int, f_column: int, i_bias: torch.Tensor, f_bias: torch.Tensor,
+                 cap: float, top: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor):
+    """Stabilized exponential gates of a matrix memory. From pre-activations (columns i_column + h and
+    f_column + h of gates [T, W]): i = cap tanh((. + i_bias) / cap), f = logsigmoid(cap tanh((. +
+    f_bias) / cap)); the running maximum m <- max(f + m, i) is carried in `top` float32 [slots, H].
+    -> decay = exp(f + m_before - m), take = exp(i - m), floor = exp(-m), float32 [T,H] each."""
+    _check(gates, "gates", dims=2)
+    _check(i_bias, "i_bias", torch.float32, 1)
+    _check(f_bias, "f_bias", torch.float32, 1)
+    _check(top, "top", torch.float32, 2)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(slots, "slots", torch.int32, 1)
+    T, H = gates.shape[0], i_bias.numel()
+    if f_bias.numel() != H or top.shape[1] != H or max(i_column, f_column) + H > gates.shape[1]:
+        raise InvalidError("capped_gates: shapes do not agree")
+    decay, take, floor = (_f32((T, H), gates.device) for _ in range(3))
+    _done(_lib().lrm_mlstm_gates(_ptr(gates), _code(gates.dtype), ctypes.c_longlong(gates.shape[1]), i_column,
+                                 f_column, _ptr(i_bias), _ptr(f_bias), ctypes.c_float(cap), _ptr(top),
+                                 _ptr(cu_seqlens), _ptr(slots), _ptr(decay), _ptr(take), _ptr(floor), slots.numel(), H,
+                                 _stream()), "capped_gates")
+    return decay, take, floor
+
+
+def memory_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, take: torch.Tensor, q_scale: float,
+                   heads: int, head_dim: int, value_dim: int, padded: int):
+    """Float32 inputs of a matrix memory's scan from its projection [T, W]: q (heads * head_dim columns
+    at q_off) times q_scale, k, and v' = take [v | 1 | 0 ..] of `padded` > value_dim columns per head:
+    the 1 carries the normalizer through the scan as one more value column.
+    -> q, k [T,H,d], v' [T,H,padded]."""
+    _check(proj, "proj", dims=2)
+    _check(take, "take", torch.float32, 2)
+    T = proj.shape[0]
+    if (tuple(take.shape) != (T, heads) or padded <= value_dim
+            or max(q_off, k_off) + heads * head_dim > proj.shape[1] or v_off + heads * value_dim > proj.shape[1]):
+        raise InvalidError("memory_prepare: shapes do not agree")
+    dev = proj.device
+    q, k = _f32((T, heads, head_dim), dev), _f32((T, heads, head_dim), dev)
+    v = _f32((T, heads, padded), dev)
+    _done(_lib().lrm_mlstm_prepare(_ptr(proj), _code(proj.dtype), ctypes.c_longlong(proj.shape[1]), q_off, k_off,
+                                   v_off, _ptr(take), ctypes.c_float(q_scale), _ptr(q), _ptr(k), _ptr(v), T, heads,
+                                   head_dim, value_dim, padded, _stream()), "memory_prepare")
+    return q, k, v
 
 
 def short_conv(src: torch.Tensor, column: int, channels: int, in_bias: Optional[torch.Tensor], taps: torch.Tensor,
@@ -575,7 +753,7 @@ def blockwise_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
                      x_column: int = 0, x_block: Optional[int] = None, out: Optional[torch.Tensor] = None,
                      out_column: int = 0, out_block: Optional[int] = None) -> torch.Tensor:
     """out[t, b, :] = (weight[b] . x[t, b, :] + bias[b]) * row_scale[t, b] with weight [B, n, m] ([out,
-    in] per block), bias float32 [B, n], row_scale float32 [T, B]. Block b of row t of x [T, W] starts
+    in] per block), bias float32 [B, n], row_scale float32 [T, B] (or [T, B * n]: one factor per output). Block b of row t of x [T, W] starts
     at column x_column + b * x_block (default: m, blocks side by side); the result goes to a new
     [T, B * n] tensor in out_dtype, or into `out` [T, W'] at column out_column + b * out_block."""
     _check(x, "x", dims=2)
@@ -591,8 +769,8 @@ def blockwise_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
             raise InvalidError("blockwise_linear: bias must be [blocks, out]")
     if row_scale is not None:
         _check(row_scale, "row_scale", torch.float32, 2)
-        if tuple(row_scale.shape) != (T, B):
-            raise InvalidError("blockwise_linear: row_scale must be [T, blocks]")
+        if tuple(row_scale.shape) not in ((T, B), (T, B * n)):
+            raise InvalidError("blockwise_linear: row_scale must be [T, blocks] or [T, blocks * out]")
     if out is None:
         out = _activation(T, B * n, out_dtype or x.dtype, x.device)
         out_column, out_block = 0, n
@@ -603,7 +781,8 @@ def blockwise_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch
             raise InvalidError("blockwise_linear: blocks outside the output row")
     _done(_lib().lrm_blockwise_linear(_column_ptr(x, x_column), _code(x.dtype), ctypes.c_longlong(x.shape[1]),
                                       ctypes.c_longlong(x_block), _ptr(weight), _code(weight.dtype), _ptr(bias),
-                                      _ptr(row_scale), _column_ptr(out, out_column), _code(out.dtype),
+                                      _ptr(row_scale), n if row_scale is not None and row_scale.shape[1] == B * n
+                                      and n > 1 else 1, _column_ptr(out, out_column), _code(out.dtype),
                                       ctypes.c_longlong(out.shape[1]), ctypes.c_longlong(out_block), T, B, n, m,
                                       _stream()), "blockwise_linear")
     return out
@@ -629,20 +808,22 @@ def rope_heads(src: torch.Tensor, src_column: int, src_head: int, dst: torch.Ten
     return dst
 
 
-def latent_prepare(proj: torch.Tensor, q_column: int, q_weight: torch.Tensor, c_column: int,
+def latent_prepare(proj: torch.Tensor, q_column: int, q_weight: Optional[torch.Tensor], c_column: int,
                    c_weight: Optional[torch.Tensor], rot: int, positions: torch.Tensor,
                    inv_freq: Optional[torch.Tensor], eps: float, gate_column: int, heads: int,
                    out_dtype: torch.dtype, kv=None, dest_rows: Optional[torch.Tensor] = None,
-                   keep_packed: bool = True):
-    """From a fused down-projection [T, W]: the normed query latent [T, q_rank] (out_dtype), the gates
-    sigmoid(.) float32 [T, heads], and, when the row has key/value columns (c_column >= 0), the rows
+                   keep_packed: bool = True, q_width: int = 0):
+    """From a fused down-projection [T, W]: the normed query latent [T, q_rank] (out_dtype; without
+    `q_weight` the `q_width` query columns as they are, for queries that have no latent), the gates
+    sigmoid(.) float32 [T, heads] (`heads`: how many gate columns there are), and, when the row has key/value columns (c_column >= 0), the rows
     [RMSnorm(latent) * c_weight | rotated shared key part] [T, kv_rank + rot], returned when
     `keep_packed` and written into the paged cache view `kv` (one key head of that width) at
     `dest_rows`. Norm weights float32. -> (cq, rows or None, gate)."""
     _check(proj, "proj", dims=2)
-    _check(q_weight, "q_weight", torch.float32, 1)
+    if q_weight is not None:
+        _check(q_weight, "q_weight", torch.float32, 1)
     _check(positions, "positions", torch.int32, 1)
-    T, q_rank = proj.shape[0], q_weight.numel()
+    T, q_rank = proj.shape[0], q_weight.numel() if q_weight is not None else q_width
     kv_rank = 0
     if c_column >= 0:
         _check(c_weight, "c_weight", torch.float32, 1)
@@ -679,16 +860,29 @@ GATE_SILU, GATE_SIGMOID = 1, 2
 
 def head_norm_gate(o: torch.Tensor, eps: float, out_dtype: torch.dtype, weight: Optional[torch.Tensor] = None,
                    gate: Optional[torch.Tensor] = None, gate_column: int = 0, gate_act: int = GATE_SILU,
-                   out_scale: float = 1.0) -> torch.Tensor:
+                   out_scale: float = 1.0, value_dim: Optional[int] = None, floor: Optional[torch.Tensor] = None,
+                   floor_eps: float = 0.0) -> torch.Tensor:
     """Per token and head: o / sqrt(mean(o^2) + eps) [* weight] [* act(gate)] * out_scale, o float32
     [T,H,dv] -> [T, H*dv] in `out_dtype`. `gate` is a [T, W] activation whose columns gate_column ..
-    gate_column + H*dv hold the gate's pre-activation; act: GATE_SILU or GATE_SIGMOID."""
+    gate_column + H*dv hold the gate's pre-activation; act: GATE_SILU or GATE_SIGMOID. `weight`
+    float32 [dv] (shared by the heads) or [H*dv]. `value_dim` < o.shape[2]: only the first value_dim
+    columns of a head are values. With `floor` float32 [T,H] a head is first divided by
+    max(|o[value_dim]|, floor) + floor_eps: column value_dim is then a normalizer's read-out."""
     _check(o, "o", torch.float32, 3)
-    T, H, dv = o.shape
+    T, H, o_stride = o.shape
+    dv = o_stride if value_dim is None else value_dim
+    if not 0 < dv <= o_stride or (floor is not None and dv == o_stride):
+        raise InvalidError("head_norm_gate: value_dim outside the head's row")
+    w_stride = 0
     if weight is not None:
         _check(weight, "weight", torch.float32, 1)
-        if weight.numel() != dv:
-            raise InvalidError("head_norm_gate: weight must have one entry per value dimension")
+        if weight.numel() not in (dv, H * dv):
+            raise InvalidError("head_norm_gate: weight must have one entry per value dimension, or per head and dimension")
+        w_stride = dv if weight.numel() == H * dv and H > 1 else 0
+    if floor is not None:
+        _check(floor, "floor", torch.float32, 2)
+        if tuple(floor.shape) != (T, H):
+            raise InvalidError("head_norm_gate: floor must be [T,H]")
     gate_ptr, stride = ctypes.c_void_p(0), 0
     gate_code = _code(out_dtype)
     if gate is not None:
@@ -698,7 +892,8 @@ def head_norm_gate(o: torch.Tensor, eps: float, out_dtype: torch.dtype, weight: 
             raise InvalidError("head_norm_gate: gate columns outside the activation")
         gate_ptr, stride = _column_ptr(gate, gate_column), gate.shape[1]
     out = _activation(T, H * dv, out_dtype, o.device)
-    _done(_lib().lrm_head_norm_gate(_ptr(o), _ptr(weight), gate_ptr, gate_code, ctypes.c_longlong(stride), gate_act, _ptr(out),
+    _done(_lib().lrm_head_norm_gate(_ptr(o), o_stride, _ptr(weight), w_stride, _ptr(floor), ctypes.c_float(floor_eps),
+                                    gate_ptr, gate_code, ctypes.c_longlong(stride), gate_act, _ptr(out),
                                     _code(out_dtype), T, H, dv, ctypes.c_float(eps), ctypes.c_float(out_scale),
                                     _stream()), "head_norm_gate")
     return out
@@ -722,10 +917,67 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int):
     return ids, weights
 
 
-def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+@dataclass(frozen=True)
+class Scoring:
+    """A router that scores with the softmax over all its outputs: the choice is made on the scores
+    plus `correction` (float32 [E] or None), among the outputs of the `keep` best of `groups` equal
+    groups of neighbours (a group counts by its largest corrected score); the weights are the
+    chosen scores, divided by their sum with `renormalize`."""
+
+    correction: Optional[torch.Tensor] = None
+    groups: int = 1
+    keep: int = 1
+    renormalize: bool = False
+
+    def arguments(self):
+        return _ptr(self.correction), self.groups, self.keep, int(self.renormalize)
+
+
+def moe_route_scored(logits: torch.Tensor, top: int, scoring: Scoring):
+    """The scored router's choice from float32 logits [T, E]. -> ids int32 [T, top], weights float32
+    [T, top]."""
+    _check(logits, "logits", torch.float32, 2)
+    T, E = logits.shape
+    _check_scoring(scoring, E, top)
+    ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    weights = _f32((T, top), logits.device)
+    _done(_lib().lrm_moe_route_scored(_ptr(logits), _ptr(scoring.correction), _ptr(ids), _ptr(weights), T, E, top,
+                                      scoring.groups, scoring.keep, int(scoring.renormalize), _stream()),
+          "moe_route_scored")
+    return ids, weights
+
+
+def _check_scoring(scoring: Scoring, E: int, top: int) -> None:
+    if scoring.correction is not None:
+        _check(scoring.correction, "correction", torch.float32, 1)
+        if scoring.correction.numel() != E:
+            raise InvalidError("router: one correction per output")
+    g, k = scoring.groups, scoring.keep
+    if g <= 0 or E % g or not 0 < k <= g or not 0 < top <= k * (E // g):
+        raise InvalidError("router: groups must divide the outputs, and the kept groups hold at least `top` of them")
+
+
+def moe_identity_add_(out: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                      experts: int) -> torch.Tensor:
+    """out[t] += (sum of weights[t, c] over the choices with ids[t, c] >= experts) * x[t]: the share of
+    identity experts, which return their input. out float32 [T, width]; x [T, width]."""
+    _check(out, "out", torch.float32, 2)
+    _check(x, "x", dims=2)
+    _check(ids, "ids", torch.int32, 2)
+    _check(weights, "weights", torch.float32, 2)
+    if x.shape != out.shape or ids.shape[0] != out.shape[0] or weights.shape != ids.shape:
+        raise InvalidError("moe_identity_add_: shapes do not agree")
+    _done(_lib().lrm_moe_identity_add(_ptr(out), _ptr(x), _code(x.dtype), _ptr(ids), _ptr(weights), out.shape[0],
+                                      out.shape[1], experts, ids.shape[1], _stream()), "moe_identity_add_")
+    return out
+
+
+def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], top: int,
+               scoring: Optional[Scoring] = None):
     """moe_route(x . weight^T, bias, top) in one launch: float32 logits from x [T, width] (float32, or
     bfloat16 widened exactly) and float32 weight [E, width], a CTA per token. For steps of few
-    tokens; None where the kernel does not take the sizes (the caller makes the product and routes)."""
+    tokens; None where the kernel does not take the sizes (the caller makes the product and routes).
+    With `scoring` the choice is the scored router's (moe_route_scored) and `bias` is not used."""
     _check(x, "x", dims=2)
     _check(weight, "weight", torch.float32, 2)
     T, width = x.shape
@@ -734,20 +986,28 @@ def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
         raise InvalidError("moe_router: shapes do not agree")
     if bias is not None:
         _check(bias, "bias", torch.float32, 1)
-    if 4 * (width + E) > 48 * 1024:
+    if scoring is not None:
+        _check_scoring(scoring, E, top)
+    if 4 * (width + (3 * E + scoring.groups // 4 + 1 if scoring is not None else E)) > 48 * 1024:
         return None
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = _f32((T, top), x.device)
+    extra = (1, *scoring.arguments()) if scoring is not None else (0, None, 1, 1, 0)
     _done(_lib().lrm_moe_router(_ptr(x), _code(x.dtype), _ptr(weight), _ptr(bias), _ptr(ids), _ptr(weights), None,
-                                T, width, E, top, _stream()), "moe_router")
+                                T, width, E, top, *extra, _stream()), "moe_router")
     return ids, weights
 
 
+ACT_CLAMPED_GATE, ACT_SILU = 0, 1
+
+
 def moe_experts_rows(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor,
-                     weights: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+                     weights: torch.Tensor, limit: float, alpha: float, act: int = ACT_CLAMPED_GATE,
+                     x32: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Every token's chosen experts, token by token: planes float32 [n, T, width] whose sum in plane
     order is sum_c weights[t,c] * expert_ids[t,c](x[t]). gate_up [E, 2 ff, width] (an expert's gate
-    rows, then its up rows), down [width, E, ff]."""
+    rows, then its up rows), down [width, E, ff]. An id of E or more is an identity expert: its
+    output is its input (x32, float32 [T, width], where the caller has the input unrounded)."""
     _check(x, "x", dims=2)
     T, width = x.shape
     _check(gate_up, "gate_up", dims=3)
@@ -762,17 +1022,22 @@ def moe_experts_rows(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor,
         raise InvalidError("moe_experts_rows: one row of choices per token")
     if T > 65535:
         raise UnsupportedError("moe_experts_rows: more than 65535 tokens in one step")
+    if x32 is not None:
+        _check(x32, "x32", torch.float32, 2)
+        if x32.shape != x.shape:
+            raise InvalidError("moe_experts_rows: x32 must match x")
     lib = _lib()
     slices = int(lib.lrm_moe_rows_slices(T, top, ff))
     planes = _f32((top * slices, T, width), x.device)
     _done(lib.lrm_moe_experts_rows(_ptr(x), _code(x.dtype), _ptr(gate_up), _ptr(down), _code(gate_up.dtype),
                                    _ptr(ids), _ptr(weights), _ptr(planes), T, width, ff, E, top, slices,
-                                   ctypes.c_float(limit), ctypes.c_float(alpha), _stream()), "moe_experts_rows")
+                                   ctypes.c_float(limit), ctypes.c_float(alpha), act, _ptr(x32), _stream()),
+          "moe_experts_rows")
     return planes
 
 
 def moe_dense_gate(gate_up: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, experts: int, limit: float,
-                   alpha: float, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                   alpha: float, out_dtype: Optional[torch.dtype] = None, act: int = ACT_CLAMPED_GATE) -> torch.Tensor:
     """From every expert's gate and up for every token, [T, E * 2 ff] (an expert's ff gate columns,
     then its ff up columns; float32, or the output's type): y [T, E * ff] = weight(t, e) * act(gate,
     up) in `out_dtype` (default: the input's), zero where token t did not choose expert e."""
@@ -786,7 +1051,7 @@ def moe_dense_gate(gate_up: torch.Tensor, ids: torch.Tensor, weights: torch.Tens
     out_dtype = out_dtype or gate_up.dtype
     y = _activation(T, experts * ff, out_dtype, gate_up.device)
     _done(_lib().lrm_moe_dense_gate(_ptr(gate_up), _code(gate_up.dtype), _code(out_dtype), _ptr(ids), _ptr(weights), _ptr(y), T, ff,
-                                    experts, top, ctypes.c_float(limit), ctypes.c_float(alpha), _stream()),
+                                    experts, top, ctypes.c_float(limit), ctypes.c_float(alpha), act, _stream()),
           "moe_dense_gate")
     return y
 

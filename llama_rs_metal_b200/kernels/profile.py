@@ -95,7 +95,7 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_delta_prepare": lambda a: (
         _v(a[20]) * ((2 * _v(a[23]) * _v(a[24]) + _v(a[22]) * _v(a[25])) * (_ELEM[_v(a[1])] + 4.0)
                      + _v(a[22]) * (_v(a[24]) * 8.0 + 4.0)), 0),
-    "lrm_head_norm_gate": lambda a: (_v(a[8]) * _v(a[9]) * _v(a[10]) * (4.0 + _ELEM[_v(a[3])] + _ELEM[_v(a[7])]), 0),
+    "lrm_head_norm_gate": lambda a: (_v(a[12]) * _v(a[13]) * _v(a[14]) * (4.0 + _ELEM[_v(a[7])] + _ELEM[_v(a[11])]), 0),
     "lrm_qkv_bias_store": lambda a: (2.0 * _v(a[9]) * (_v(a[10]) * _v(a[12]) + _v(a[11]) * (_v(a[12]) + _v(a[13])))
                                      * _ELEM[_v(a[1])], 0),
     # token by token: an expert's three matrices once per (token, choice) that reads them, at most once
@@ -117,12 +117,31 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_gated_linear_scan": lambda a: (hints["tokens"] * _v(a[14]) * (2.0 * _ELEM[_v(a[1])] + 12.0) + 8.0 * _v(a[12]) * _v(a[14]),
                                         30.0 * hints["tokens"] * _v(a[14])),
     "lrm_blockwise_linear": lambda a: (
-        _v(a[12]) * _v(a[13]) * (_v(a[15]) * _ELEM[_v(a[1])] + _v(a[14]) * _ELEM[_v(a[9])])
-        + _v(a[13]) * _v(a[14]) * _v(a[15]) * _ELEM[_v(a[5])], 2.0 * _v(a[12]) * _v(a[13]) * _v(a[14]) * _v(a[15])),
+        _v(a[13]) * _v(a[14]) * (_v(a[16]) * _ELEM[_v(a[1])] + _v(a[15]) * _ELEM[_v(a[10])])
+        + _v(a[14]) * _v(a[15]) * _v(a[16]) * _ELEM[_v(a[5])], 2.0 * _v(a[13]) * _v(a[14]) * _v(a[15]) * _v(a[16])),
     "lrm_rope_heads": lambda a: (2.0 * _v(a[10]) * _v(a[11]) * _v(a[9]) * _ELEM[_v(a[1])], 0),
     "lrm_latent_prepare": lambda a: (
         _v(a[21]) * ((_v(a[4]) + (_v(a[7]) + _v(a[9]) if _v(a[6]) >= 0 else 0)) * (_ELEM[_v(a[1])] + _ELEM[_v(a[20])])
                      + 8.0 * _v(a[18])), 0),
+    # a norm with weight and bias: the rows read, the result written; behind a sublayer also the stream
+    # read and written and, where asked for, its rounding written
+    "lrm_layer_norm": lambda a: (_v(a[6]) * _v(a[7]) * (4.0 + _ELEM[_v(a[4])]), 8.0 * _v(a[6]) * _v(a[7])),
+    "lrm_layer_norm_add": lambda a: (_v(a[7]) * _v(a[8]) * (12.0 + (_ELEM[_v(a[6])] if a[5].value else 0)),
+                                     10.0 * _v(a[7]) * _v(a[8])),
+    "lrm_relu_squared": lambda a: (_v(a[4]) * (_ELEM[_v(a[1])] + _ELEM[_v(a[3])]), 0),
+    # the state-space mixer's inputs: the convolved channels read (taps times, from cache) and written
+    # in float32 (x twice), the decays; its read-out: o, x and z read, the result written
+    "lrm_ssd_prepare": lambda a: (
+        _v(a[19]) * ((_v(a[20]) * _v(a[23]) + 2 * _v(a[21]) * _v(a[22])) * _ELEM[_v(a[1])]
+                     + 4.0 * (2 * _v(a[20]) * _v(a[23]) + 2 * _v(a[21]) * _v(a[22]) + _v(a[20]))),
+        2.0 * _v(a[19]) * (_v(a[20]) * _v(a[23]) + 2 * _v(a[21]) * _v(a[22])) * _v(a[9])),
+    "lrm_skip_gate_part_norm": lambda a: (_v(a[9]) * _v(a[10]) * (8.0 + _ELEM[_v(a[4])] + _ELEM[_v(a[8])]), 0),
+    "lrm_conv_tail_update": lambda a: (0, 0),
+    "lrm_mlstm_gates": lambda a: (hints["tokens"] * _v(a[15]) * (2.0 * _ELEM[_v(a[1])] + 12.0), 0),
+    "lrm_mlstm_prepare": lambda a: (
+        _v(a[11]) * _v(a[12]) * ((2 * _v(a[13]) + _v(a[14])) * _ELEM[_v(a[1])] + 4.0 * (2 * _v(a[13]) + _v(a[15]))), 0),
+    "lrm_moe_route_scored": lambda a: (_v(a[4]) * (_v(a[5]) * 4.0 + _v(a[6]) * 8.0), 0),
+    "lrm_moe_identity_add": lambda a: (_v(a[5]) * _v(a[6]) * (8.0 + _ELEM[_v(a[2])]), 0),
     "lrm_sample_gumbel_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
 }
 # entry points that only answer questions and launch nothing

@@ -1,19 +1,21 @@
 from .base import (Block, CompositeRequest, FeedForward, KeyValueRequest, LayerSpec, Mixer, ModelPlan, Norm,
                    Part, PartSpec, PositionEncoding, ScheduleEntry, StateRequest)
 from .linear import LinearWeight
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm, StreamCast
 from .rope import DistancePenalty, RotaryEmbedding
 from .attention import Attention
-from .mlp import GatedMLP
-from .recurrent import GatedDeltaRule, GatedLinearRecurrence, Retention
+from .mlp import GatedMLP, PlainMLP
+from .recurrent import GatedDeltaRule, GatedLinearRecurrence, MatrixMemory, Retention, StateSpaceDuality
 from .latent import LatentAttention
 from .parallel import ParallelMixer
 from .moe import MixtureOfExperts
-from .block import PreNormBlock, PreNormMixerBlock, SandwichNormBlock, SandwichNormMixerBlock
+from .block import (PostNormBlock, PostNormMixerBlock, PreNormBlock, PreNormMixerBlock, SandwichNormBlock,
+                    SandwichNormMixerBlock)
 
 __all__ = ["Block", "CompositeRequest", "FeedForward", "KeyValueRequest", "LayerSpec", "Mixer", "ModelPlan", "Norm",
            "Part", "PartSpec", "PositionEncoding", "ScheduleEntry", "StateRequest", "LinearWeight",
            "RMSNorm", "RotaryEmbedding", "DistancePenalty", "Attention", "GatedMLP", "Retention", "GatedDeltaRule",
            "GatedLinearRecurrence", "LatentAttention",
            "ParallelMixer", "MixtureOfExperts", "PreNormBlock", "PreNormMixerBlock", "SandwichNormBlock",
-           "SandwichNormMixerBlock"]
+           "SandwichNormMixerBlock", "LayerNorm", "StreamCast", "PlainMLP", "StateSpaceDuality", "MatrixMemory",
+           "PostNormBlock", "PostNormMixerBlock"]

@@ -3,6 +3,9 @@ from __future__ import annotations
 
 from ..registry import register_block
 from .base import Block
+from .norm import StreamCast
+
+STREAM_ITSELF = StreamCast()  # what a block whose sublayers read the stream itself has for an entry norm
 
 
 @register_block("pre_norm")
@@ -100,5 +103,62 @@ class SandwichNormMixerBlock(_SandwichBlock):
     def forward(self, hidden, ctx, cache):
         following = ctx.next_entry_norm
         normed = self._mixer_half(hidden, ctx, cache, following)
+        ctx.normed = (following, normed) if following is not None else None
+        return hidden
+
+
+class _PostNormBlock(Block):
+    """A norm on each sublayer's output only, and a factor on what it adds:
+    hidden += mult * post_norm(sublayer(hidden)). The sublayers read the stream itself (its rounding
+    under bfloat16 activations, which the pass of the norm before writes beside the float32 row);
+    a sublayer's output stays float32 up to its norm. While a sublayer runs, ctx.stream is the
+    float32 stream its input is the rounding of."""
+
+    graph_safe = True
+
+    def __init__(self, residual_mult: float = 1.0, **parts):
+        super().__init__(**parts)
+        self.residual_mult = float(residual_mult)
+
+    @property
+    def entry_norm(self):
+        return STREAM_ITSELF
+
+    def _mixer_half(self, hidden, ctx, cache, then):
+        x = ctx.take_normed(STREAM_ITSELF)
+        if x is None:
+            x = STREAM_ITSELF.forward(hidden, ctx)
+        ctx.stream = hidden
+        y = self.mixer.forward(x, ctx, cache, residual=None)
+        return self.mixer_post_norm.add_into(hidden, y, ctx, self.residual_mult, then)
+
+
+@register_block("post_norm")
+class PostNormBlock(_PostNormBlock):
+    """A mixer and a feed-forward, each with a norm behind it."""
+
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_post_norm": "norm",
+             "feed_forward_post_norm": "norm"}
+
+    def forward(self, hidden, ctx, cache):
+        following = ctx.next_entry_norm
+        x = self._mixer_half(hidden, ctx, cache, STREAM_ITSELF)
+        y = self.feed_forward.forward(x, ctx, residual=None)
+        normed = self.feed_forward_post_norm.add_into(hidden, y, ctx, self.residual_mult, following)
+        ctx.stream = None
+        ctx.normed = (following, normed) if following is not None else None
+        return hidden
+
+
+@register_block("post_norm_mixer")
+class PostNormMixerBlock(_PostNormBlock):
+    """A mixer with a norm behind it: a layer without a feed-forward."""
+
+    roles = {"mixer": "mixer", "mixer_post_norm": "norm"}
+
+    def forward(self, hidden, ctx, cache):
+        following = ctx.next_entry_norm
+        normed = self._mixer_half(hidden, ctx, cache, following)
+        ctx.stream = None
         ctx.normed = (following, normed) if following is not None else None
         return hidden

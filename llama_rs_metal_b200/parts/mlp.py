@@ -1,4 +1,4 @@
-"""Dense gated feed-forward."""
+"""Dense feed-forwards: gated, and plain (one matrix up, an activation, one matrix down)."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -59,3 +59,31 @@ class GatedMLP(FeedForward):
         else:
             gated = ops.silu_mul(self.gate_up(x), self.block)
         return self.down(gated, epilogue=ops.ADD, out=residual, ctx=ctx)
+
+
+@register_feed_forward("mlp")
+class PlainMLP(FeedForward):
+    """down( act(x Wu^T) ) without a gate; activation "relu_squared": act(z) = max(z, 0)^2. The
+    first product keeps its float32 sums up to the activation (squaring doubles a rounding's
+    relative size)."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu_squared"):
+        if activation != "relu_squared":
+            raise UnsupportedError(f"feed-forward activation {activation!r}")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.up: Optional[LinearWeight] = None
+        self.down: Optional[LinearWeight] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        h, i = self.hidden_size, self.intermediate_size
+        return {"up_proj.weight": TensorSpec((i, h)), "down_proj.weight": TensorSpec((h, i))}
+
+    def bind(self, weights, runtime) -> None:
+        self.up = LinearWeight(weights["up_proj.weight"])
+        self.down = LinearWeight(weights["down_proj.weight"])
+
+    def forward(self, x, ctx, residual):
+        inner = ops.relu_squared(self.up(x, out_dtype=torch.float32), x.dtype)
+        return self.down(inner, epilogue=ops.ADD, out=residual, ctx=ctx)

@@ -1,15 +1,15 @@
 """Mixture of experts: a router picks a few small gated feed-forwards per token."""
 from __future__ import annotations
 
-from typing import Dict, Optional
+from typing import Dict, Optional, Tuple
 
 import torch
 
 from ..errors import InvalidError, UnsupportedError
 from ..kernels import ops
-from ..registry import register_feed_forward
+from ..registry import FEED_FORWARDS, build_part, register_feed_forward
 from ..weights.loader import TensorSpec
-from .base import FeedForward
+from .base import FeedForward, PartSpec
 from .linear import LinearWeight
 
 
@@ -30,7 +30,17 @@ class MixtureOfExperts(FeedForward):
     next norm where it folds them). All experts at once (bfloat16 steps of DENSE_ROWS tokens and
     more when at most DENSE_RATIO experts exist per chosen one): two tensor-core products over
     every expert, with the weights of the experts a token did not choose set to zero between
-    them."""
+    them.
+
+    Options beyond that router and that expert. `activation` "silu": an expert is W_down (silu(W_gate
+    x) * (W_up x)). `scoring` "softmax_all": the scores are s = softmax(z) over all outputs; the
+    choice is made on s + correction (`correction` True: a stored vector), the weights are the
+    chosen s (divided by their sum with `renormalize`). `groups` (count, keep): the outputs form
+    `count` equal groups of neighbours, a group counts by its largest choice score, and only the
+    outputs of the `keep` best groups can be chosen. `identity` n: the router has n more outputs
+    than there are experts; the last n are identity experts without matrices, whose output is the
+    layer's input itself (the float32 stream where the block gives it) times the weight. `shared`
+    (a PartSpec of a feed-forward): a part that runs for every token and is added."""
 
     graph_safe = True
     ROUTER_ROWS = 256  # up to this many tokens the router always runs as one launch, a CTA per token
@@ -39,22 +49,44 @@ class MixtureOfExperts(FeedForward):
 
     def __init__(self, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
                  activation: str = "clamped_gate", limit: float = 7.0, alpha: float = 1.702,
-                 router_bias: bool = True):
-        if activation != "clamped_gate":
+                 router_bias: bool = True, scoring: str = "softmax_chosen", correction: bool = False,
+                 groups: Optional[Tuple[int, int]] = None, renormalize: bool = False, identity: int = 0,
+                 shared: Optional[PartSpec] = None):
+        if activation not in ("clamped_gate", "silu"):
             raise UnsupportedError(f"expert activation {activation!r}")
-        if num_experts <= 0 or not 0 < top <= num_experts:
+        if scoring not in ("softmax_chosen", "softmax_all"):
+            raise UnsupportedError(f"router scoring {scoring!r}")
+        outputs = num_experts + identity
+        if num_experts <= 0 or identity < 0 or not 0 < top <= outputs:
             raise InvalidError("the router chooses between 1 and all of the experts")
+        count, keep = groups if groups is not None else (1, 1)
+        if scoring == "softmax_chosen" and (correction or groups is not None or identity or renormalize):
+            raise UnsupportedError("corrections, groups and identity experts belong to the softmax_all router")
+        if count <= 0 or outputs % count or not 0 < keep <= count or top > keep * (outputs // count):
+            raise InvalidError("router groups must divide its outputs, and the kept groups hold at least `top` of them")
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
-        self.num_experts, self.top = num_experts, top
-        self.limit, self.alpha, self.router_bias = float(limit), float(alpha), bool(router_bias)
+        self.num_experts, self.top, self.identity, self.outputs = num_experts, top, identity, outputs
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.act = ops.ACT_SILU if activation == "silu" else ops.ACT_CLAMPED_GATE
+        self.scored, self.has_correction = scoring == "softmax_all", bool(correction)
+        self.router_bias = bool(router_bias) and not self.scored
+        self.groups, self.keep, self.renormalize = count, keep, bool(renormalize)
+        self.shared = build_part(FEED_FORWARDS, shared, "feed-forward") if shared is not None else None
+        self._shared_spec = shared
         self.router: Optional[LinearWeight] = None
         self.bias: Optional[torch.Tensor] = None
+        self.scoring: Optional[ops.Scoring] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
         h, f = self.hidden_size, self.intermediate_size
-        out = {"router.weight": TensorSpec((self.num_experts, h))}
+        out = {"router.weight": TensorSpec((self.outputs, h))}
         if self.router_bias:
             out["router.bias"] = TensorSpec((self.num_experts,))
+        if self.has_correction:
+            out["router.correction"] = TensorSpec((self.outputs,))
+        if self.shared is not None:
+            for own, spec in self.shared.tensors().items():
+                out["shared." + own] = spec
         for e in range(self.num_experts):
             out[f"experts.{e}.gate_proj.weight"] = TensorSpec((f, h))
             out[f"experts.{e}.up_proj.weight"] = TensorSpec((f, h))
@@ -64,6 +96,11 @@ class MixtureOfExperts(FeedForward):
     def bind(self, weights, runtime) -> None:
         self.router = LinearWeight(weights["router.weight"].to(torch.float32))
         self.bias = weights["router.bias"].to(torch.float32).contiguous() if self.router_bias else None
+        if self.scored:
+            correction = weights["router.correction"].to(torch.float32).contiguous() if self.has_correction else None
+            self.scoring = ops.Scoring(correction, self.groups, self.keep, self.renormalize)
+        if self.shared is not None:
+            self.shared.bind({own: weights["shared." + own] for own in self.shared.tensors()}, runtime)
         E, f, h = self.num_experts, self.intermediate_size, self.hidden_size
         self.gate_up = torch.stack([torch.cat([weights[f"experts.{e}.gate_proj.weight"],
                                                weights[f"experts.{e}.up_proj.weight"]]) for e in range(E)]).contiguous()
@@ -76,21 +113,49 @@ class MixtureOfExperts(FeedForward):
         """(expert ids int32 [T, top], weights float32 [T, top]). One launch per step; steps of
         many tokens make the logits with the float32 matrix kernel first when there are many
         experts to a token's CTA."""
-        routed = ops.moe_router(x, self.router.weight, self.bias, self.top) \
-            if x.shape[0] <= self.ROUTER_ROWS or self.num_experts <= 16 else None
+        routed = ops.moe_router(x, self.router.weight, self.bias, self.top, self.scoring) \
+            if x.shape[0] <= self.ROUTER_ROWS or self.outputs <= 16 else None
         if routed is None:
-            routed = ops.moe_route(self.router(x, out_dtype=torch.float32), self.bias, self.top)
+            logits = self.router(x, out_dtype=torch.float32)
+            routed = ops.moe_route_scored(logits, self.top, self.scoring) if self.scored \
+                else ops.moe_route(logits, self.bias, self.top)
         return routed
 
     def forward(self, x, ctx, residual):
         ids, weights = self.route(x)
-        if (x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] >= self.DENSE_ROWS
-                and self.num_experts <= self.DENSE_RATIO * self.top):
+        # identity experts pass the input on: the float32 stream itself where x is its rounding
+        x32 = ctx.stream if self.identity and x.dtype != torch.float32 else None
+        dense = (x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] >= self.DENSE_ROWS
+                 and self.num_experts <= self.DENSE_RATIO * self.top)
+        if residual is None:
+            # a block that puts a norm between this part and the stream: the shared part's float32
+            # output (or the all-experts product's) is what everything else is added to
+            out = self.shared.forward(x, ctx, residual=None) if self.shared is not None else None
+            if dense:
+                both = self.gate_up_all(x, out_dtype=torch.float32)
+                y = ops.moe_dense_gate(both, ids, weights, self.num_experts, self.limit, self.alpha, out_dtype=x.dtype,
+                                       act=self.act)
+                out = self.down_all(y, epilogue=ops.ADD, out=out)
+                if self.identity:
+                    ops.moe_identity_add_(out, x32 if x32 is not None else x, ids, weights, self.num_experts)
+                return out
+            planes = ops.moe_experts_rows(x, self.gate_up, self.down, ids, weights, self.limit, self.alpha, self.act, x32)
+            if out is None:
+                out, planes = planes[0], planes[1:]
+            return ops.add_planes_(out, planes) if planes.shape[0] else out
+        if self.shared is not None:
+            residual = self.shared.forward(x, ctx, residual=residual)
+            ctx.settle(residual)
+        if dense:
             # gate and up stay float32 up to the activation, as they do token by token
             both = self.gate_up_all(x, out_dtype=torch.float32)
-            y = ops.moe_dense_gate(both, ids, weights, self.num_experts, self.limit, self.alpha, out_dtype=x.dtype)
+            y = ops.moe_dense_gate(both, ids, weights, self.num_experts, self.limit, self.alpha, out_dtype=x.dtype,
+                                   act=self.act)
+            if self.identity:
+                ctx.settle(residual)
+                ops.moe_identity_add_(residual, x32 if x32 is not None else x, ids, weights, self.num_experts)
             return self.down_all(y, epilogue=ops.ADD, out=residual, ctx=ctx)
-        planes = ops.moe_experts_rows(x, self.gate_up, self.down, ids, weights, self.limit, self.alpha)
+        planes = ops.moe_experts_rows(x, self.gate_up, self.down, ids, weights, self.limit, self.alpha, self.act, x32)
         if ctx.may_defer:
             ctx.settle(residual)  # at most one set of partial sums is pending at a time
             ctx.pending = planes

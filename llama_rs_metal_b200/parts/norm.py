@@ -1,10 +1,11 @@
-"""RMSNorm."""
+"""Norms: RMSNorm, layer norm with weight and bias, and the plain rounding of the stream."""
 from __future__ import annotations
 
 from typing import Dict, Optional
 
 import torch
 
+from ..errors import UnsupportedError
 from ..kernels import ops
 from ..registry import register_norm
 from ..weights.loader import TensorSpec
@@ -51,3 +52,51 @@ class RMSNorm(Norm):
         if then is not None and not fused:
             out = then.forward(hidden, ctx)
         return out
+
+
+@register_norm("cast")
+class StreamCast(Norm):
+    """No norm at all: the stream itself in the activation type (the float32 stream as it is under
+    float32 activations, its rounding under bfloat16). It stands where a block wants "the norm in
+    front of the sublayer" of an arrangement whose sublayers read the stream itself."""
+
+    graph_safe = True
+
+    def forward(self, hidden, ctx, rows=None):
+        if rows is not None:
+            raise UnsupportedError("the plain rounding of the stream is not made for chosen rows")
+        return ops.cast(hidden, ctx.runtime.dtype)
+
+
+@register_norm("layer_norm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(variance + eps) * w + b over a row, with the variance the mean of the
+    squared deviations; statistics, weight and bias in float32. The bias is the tensor `bias`."""
+
+    graph_safe = True
+
+    def __init__(self, size: int, eps: float):
+        self.size, self.eps = size, float(eps)
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        return {"weight": TensorSpec((self.size,)), "bias": TensorSpec((self.size,))}
+
+    def bind(self, weights, runtime) -> None:
+        self.weight = weights["weight"].to(torch.float32).contiguous()
+        self.bias = weights["bias"].to(torch.float32).contiguous()
+
+    def forward(self, hidden, ctx, rows=None):
+        return ops.layer_norm(hidden, self.weight, self.bias, self.eps, ctx.runtime.dtype, rows=rows)
+
+    def add_into(self, hidden, y, ctx, mult=1.0, then=None):
+        # the pass that adds the normed output also writes the updated row in the activation type
+        # when the next sublayer reads the stream itself
+        if isinstance(then, StreamCast):
+            if ctx.runtime.dtype == torch.float32:
+                ops.layer_norm_add_(hidden, y, self.weight, self.bias, self.eps, mult)
+                return hidden
+            return ops.layer_norm_add_(hidden, y, self.weight, self.bias, self.eps, mult, cast_dtype=ctx.runtime.dtype)
+        ops.layer_norm_add_(hidden, y, self.weight, self.bias, self.eps, mult)
+        return then.forward(hidden, ctx) if then is not None else None

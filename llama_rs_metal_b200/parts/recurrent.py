@@ -13,6 +13,15 @@ A third keeps one number per channel (csrc/gated_recurrence.cu):
 * `gated_linear_recurrence`: S <- a S + sqrt(1 - a^2) (i u) with a decay a and an input gate i
   computed from the input, block by block of channels; u passes a short causal convolution first.
 
+Two more decay S by one number per head and token, S <- a_t S + k (b_t v)^T, on the same scan
+(csrc/scalar_gated_state.cu prepares their inputs and reads them out):
+
+* `state_space_duality`: a_t = exp(-exp(A_log_h) dt_t), b_t = dt_t with a step size dt computed from
+  the input; x, B (the keys) and C (the queries) pass a short causal convolution first; the read-out
+  is gated, then normalized part by part.
+* `matrix_memory`: exponential input and forget gates under a running maximum, a normalizer n
+  beside S, the read-out divided by max(|n . q|, exp(-m)).
+
 A step of any size (a prompt, a portion, one token) runs the same scan from the state the
 steps before left, so nothing depends on how a sequence was cut into steps.
 """
@@ -236,4 +245,136 @@ class GatedLinearRecurrence(Mixer):
         gates = ops.blockwise_linear(u, self.gates, bias=self.gate_bias, out_dtype=torch.float32)
         mixed = ops.gated_linear_scan(u, gates, projected, C, self.in_bias[C:], self.rate, state.state,
                                       ctx.cu_seqlens, ctx.slots, ctx.max_seq_len, self.blocks)
+        return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
+
+
+@register_mixer("state_space_duality")
+class StateSpaceDuality(Mixer):
+    """A state-space mixer with one scalar decay per head and token. With inner = heads * value_dim,
+    N = state_size and G = groups, W_in x is [z: inner | x: inner | B: G N | C: G N | dt: heads];
+    x, B and C pass a causal convolution of `conv_taps` taps per channel with a bias (zeros before
+    the start) and SiLU; dt = softplus(dt + dt_bias), without a clamp. Per head h (which reads the
+    B and C of group h // (heads / G)), with S [N, value_dim] from zero:
+        S <- exp(-exp(A_log_h) dt) S + dt B x^T,    y = S^T C + D_h x.
+    y (heads side by side) is multiplied by silu(z), then each of `norm_parts` equal parts of the
+    row is divided by its own root mean square (`eps`) and multiplied by a weight: the gate comes
+    before the norm. Then W_o. The projection keeps its float32 sums; decays, step sizes and the
+    state are float32 (csrc/scalar_gated_state.cu, the per-token-decay scan of csrc/recurrent_scan.cu).
+    State: S in float32 and the last conv_taps - 1 convolution inputs of every channel."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, value_dim: int, state_size: int, groups: int,
+                 conv_taps: int, norm_parts: int, eps: float):
+        inner = num_heads * value_dim
+        if min(num_heads, value_dim, state_size, groups, conv_taps, norm_parts) <= 0 or num_heads % groups \
+                or inner % norm_parts:
+            raise InvalidError("state-space mixer: heads must be a multiple of groups, and the inner width of the norm's parts")
+        self.hidden_size, self.num_heads, self.value_dim, self.state_size = hidden_size, num_heads, value_dim, state_size
+        self.groups, self.conv_taps, self.norm_parts, self.eps = groups, conv_taps, norm_parts, float(eps)
+        self.inner = inner
+        self.channels = inner + 2 * groups * state_size
+        self.fused: Optional[LinearWeight] = None
+        self.out: Optional[LinearWeight] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        H, h, C = self.num_heads, self.hidden_size, self.channels
+        return {"in_proj.weight": TensorSpec((self.inner + C + H, h)), "conv.weight": TensorSpec((C, self.conv_taps)),
+                "conv.bias": TensorSpec((C,)), "dt_bias": TensorSpec((H,)), "A_log": TensorSpec((H,)),
+                "D": TensorSpec((H,)), "norm.weight": TensorSpec((self.inner,)),
+                "o_proj.weight": TensorSpec((h, self.inner))}
+
+    def bind(self, weights, runtime) -> None:
+        f32 = torch.float32
+        self.fused = LinearWeight(weights["in_proj.weight"])
+        self.taps = weights["conv.weight"].to(f32).contiguous()
+        self.conv_bias = weights["conv.bias"].to(f32).contiguous()
+        self.dt_bias = weights["dt_bias"].to(f32).contiguous()
+        self.rate = torch.exp(weights["A_log"].to(f32)).contiguous()      # exp(A_log), float32
+        self.skip = weights["D"].to(f32).contiguous()
+        self.norm_weight = weights["norm.weight"].to(f32).contiguous()
+        self.out = LinearWeight(weights["o_proj.weight"])
+
+    def cache_request(self):
+        return CompositeRequest((
+            StateRequest((self.num_heads, self.state_size, self.value_dim), torch.float32),
+            StateRequest((self.conv_taps - 1, self.channels), torch.float32)))
+
+    def forward(self, x, ctx, cache, residual):
+        _needs_own_state(ctx)
+        H, G, N, dv = self.num_heads, self.groups, self.state_size, self.value_dim
+        state, tails = cache
+        projected = self.fused(x, out_dtype=torch.float32)               # [T, z | x | B | C | dt], float32
+        q, k, v, xf, decay = ops.ssd_prepare(projected, self.inner, self.inner + self.channels, self.dt_bias, self.rate,
+                                             self.taps, self.conv_bias, tails.state, ctx.cu_seqlens, ctx.seq_of_token,
+                                             ctx.slots, H, G, N, dv)
+        ops.conv_tail_update_(projected, self.inner, self.channels, self.conv_taps, tails.state, ctx.cu_seqlens,
+                              ctx.slots)
+        o = ops.linear_state_scan(q, k, v, state.state, ctx.cu_seqlens, ctx.slots, token_decay=decay)
+        mixed = ops.skip_gate_part_norm(o, xf, self.skip, projected, 0, self.norm_weight, self.norm_parts, self.eps,
+                                        x.dtype)
+        return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
+
+
+@register_mixer("matrix_memory")
+class MatrixMemory(Mixer):
+    """A matrix memory with exponential gates, stabilized by a running maximum. q = W_q x *
+    head_dim^-1/2, k = W_k x (heads x head_dim), v = W_v x (heads x value_dim); per head a log input
+    gate i = cap tanh((W_i x + b_i) / cap) and a log forget gate f = logsigmoid(cap tanh((W_f x +
+    b_f) / cap)) with cap = `gate_cap`. With S [head_dim, value_dim], n [head_dim] and m from zero:
+        m' = max(f + m, i);  S <- exp(f + m - m') S + exp(i - m') k v^T;  n likewise with k alone;
+        o = S^T q / (max(|n . q|, exp(-m')) + floor_eps).
+    Each head's o is divided by its root mean square (`eps`), multiplied by a weight over all
+    heads' columns and by sigmoid(W_g x), then W_o. The projection keeps its float32 sums; gates,
+    the maximum, S and n are float32. n rides the scan as one more value column (csrc/
+    scalar_gated_state.cu), so the state is S | n [head_dim, value_dim + 1, filled up to a multiple of
+    four columns] and m per head."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, gate_cap: float, eps: float,
+                 floor_eps: float = 1e-6):
+        if min(num_heads, head_dim, value_dim) <= 0 or not gate_cap > 0:
+            raise InvalidError("matrix memory: sizes and the gates' cap must be positive")
+        self.hidden_size, self.num_heads, self.head_dim, self.value_dim = hidden_size, num_heads, head_dim, value_dim
+        self.gate_cap, self.eps, self.floor_eps = float(gate_cap), float(eps), float(floor_eps)
+        self.padded = (value_dim + 1 + 3) // 4 * 4
+        self.fused: Optional[LinearWeight] = None
+        self.out: Optional[LinearWeight] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        H, d, dv, h = self.num_heads, self.head_dim, self.value_dim, self.hidden_size
+        return {"q_proj.weight": TensorSpec((H * d, h)), "k_proj.weight": TensorSpec((H * d, h)),
+                "v_proj.weight": TensorSpec((H * dv, h)), "g_proj.weight": TensorSpec((H * dv, h)),
+                "i_gate.weight": TensorSpec((H, h)), "i_gate.bias": TensorSpec((H,)),
+                "f_gate.weight": TensorSpec((H, h)), "f_gate.bias": TensorSpec((H,)),
+                "norm.weight": TensorSpec((H * dv,)), "o_proj.weight": TensorSpec((h, H * dv))}
+
+    def bind(self, weights, runtime) -> None:
+        f32 = torch.float32
+        # q | k | v | g | i | f in one product
+        self.fused = LinearWeight(torch.cat([weights[n + ".weight"] for n in
+                                             ("q_proj", "k_proj", "v_proj", "g_proj", "i_gate", "f_gate")], dim=0))
+        self.i_bias = weights["i_gate.bias"].to(f32).contiguous()
+        self.f_bias = weights["f_gate.bias"].to(f32).contiguous()
+        self.norm_weight = weights["norm.weight"].to(f32).contiguous()
+        self.out = LinearWeight(weights["o_proj.weight"])
+
+    def cache_request(self):
+        return CompositeRequest((StateRequest((self.num_heads, self.head_dim, self.padded), torch.float32),
+                                 StateRequest((self.num_heads,), torch.float32)))
+
+    def forward(self, x, ctx, cache, residual):
+        _needs_own_state(ctx)
+        H, d, dv = self.num_heads, self.head_dim, self.value_dim
+        state, top = cache
+        projected = self.fused(x, out_dtype=torch.float32)               # [T, q | k | v | g | i | f], float32
+        gates_at = 2 * H * d + 2 * H * dv
+        decay, take, floor = ops.capped_gates(projected, gates_at, gates_at + H, self.i_bias, self.f_bias,
+                                              self.gate_cap, top.state, ctx.cu_seqlens, ctx.slots)
+        q, k, v = ops.memory_prepare(projected, 0, H * d, 2 * H * d, take, d ** -0.5, H, d, dv, self.padded)
+        o = ops.linear_state_scan(q, k, v, state.state, ctx.cu_seqlens, ctx.slots, token_decay=decay)
+        mixed = ops.head_norm_gate(o, self.eps, x.dtype, weight=self.norm_weight, gate=projected,
+                                   gate_column=2 * H * d + H * dv, gate_act=ops.GATE_SIGMOID, value_dim=dv,
+                                   floor=floor, floor_eps=self.floor_eps)
         return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
