@@ -34,16 +34,23 @@ __device__ __forceinline__ void row_statistics(const float (&v)[PER], int hidden
   *inv_out = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(hidden) + eps);
 }
 
+// Rows of up to 8 elements per thread take weight and bias into registers ahead of the wait;
+// longer rows (PER 32, up to 1024 threads) read them where they are used, which keeps the kernel
+// within the registers 1024 threads can have.
 template <typename O, int PER>
-__global__ void layer_norm_kernel(const float* x, const float* __restrict__ w, const float* __restrict__ b, O* out,
+__global__ __launch_bounds__(1024) void layer_norm_kernel(const float* x, const float* __restrict__ w, const float* __restrict__ b, O* out,
                                   const int* rows, int hidden, float eps) {
   __shared__ float scratch[32];
-  float wv[PER], bv[PER];
+  constexpr bool EARLY = PER <= 8;
+  constexpr int KEPT = EARLY ? PER : 1;
+  float wv[KEPT], bv[KEPT];
+  if (EARLY) {
 #pragma unroll
-  for (int e = 0; e < PER; ++e) {  // weights do not depend on the kernel before this one
-    const int i = threadIdx.x + e * blockDim.x;
-    wv[e] = i < hidden ? w[i] : 0.f;
-    bv[e] = i < hidden ? b[i] : 0.f;
+    for (int e = 0; e < KEPT; ++e) {  // weights do not depend on the kernel before this one
+      const int i = threadIdx.x + e * blockDim.x;
+      wv[e] = i < hidden ? w[i] : 0.f;
+      bv[e] = i < hidden ? b[i] : 0.f;
+    }
   }
   pdl_trigger();
   pdl_wait();
@@ -60,20 +67,25 @@ __global__ void layer_norm_kernel(const float* x, const float* __restrict__ w, c
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
     const int i = threadIdx.x + e * blockDim.x;
-    if (i < hidden) out[dst + i] = from_f32<O>(fmaf((v[e] - mean) * inv, wv[e], bv[e]));
+    if (i < hidden)
+      out[dst + i] = from_f32<O>(fmaf((v[e] - mean) * inv, EARLY ? wv[e % KEPT] : w[i], EARLY ? bv[e % KEPT] : b[i]));
   }
 }
 
 template <typename O, int PER>
-__global__ void layer_norm_add_kernel(float* stream, const float* y, const float* __restrict__ w,
+__global__ __launch_bounds__(1024) void layer_norm_add_kernel(float* stream, const float* y, const float* __restrict__ w,
                                       const float* __restrict__ b, float mult, O* cast_out, int hidden, float eps) {
   __shared__ float scratch[32];
-  float wv[PER], bv[PER];
+  constexpr bool EARLY = PER <= 8;
+  constexpr int KEPT = EARLY ? PER : 1;
+  float wv[KEPT], bv[KEPT];
+  if (EARLY) {
 #pragma unroll
-  for (int e = 0; e < PER; ++e) {
-    const int i = threadIdx.x + e * blockDim.x;
-    wv[e] = i < hidden ? w[i] : 0.f;
-    bv[e] = i < hidden ? b[i] : 0.f;
+    for (int e = 0; e < KEPT; ++e) {
+      const int i = threadIdx.x + e * blockDim.x;
+      wv[e] = i < hidden ? w[i] : 0.f;
+      bv[e] = i < hidden ? b[i] : 0.f;
+    }
   }
   pdl_trigger();
   pdl_wait();
@@ -90,14 +102,16 @@ __global__ void layer_norm_add_kernel(float* stream, const float* y, const float
   for (int e = 0; e < PER; ++e) {
     const int i = threadIdx.x + e * blockDim.x;
     if (i < hidden) {
-      const float updated = stream[row + i] + mult * fmaf((v[e] - mean) * inv, wv[e], bv[e]);
+      const float updated = stream[row + i] + mult * fmaf((v[e] - mean) * inv, EARLY ? wv[e % KEPT] : w[i],
+                                                          EARLY ? bv[e % KEPT] : b[i]);
       stream[row + i] = updated;
       if (cast_out != nullptr) cast_out[row + i] = from_f32<O>(updated);
     }
   }
 }
 
-int row_threads(int hidden) { return hidden > 4096 ? 1024 : (hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 32)); }
+// short rows on 32 to 256 threads, rows beyond 2048 elements on 1024
+int row_threads(int hidden) { return hidden > 2048 ? 1024 : (hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 32)); }
 
 }  // namespace
 

@@ -209,6 +209,100 @@ def make_pibuvik_dir(path, name, dtype=torch.bfloat16):
     return write_model_folder(path, config.to_dict(), tensors, spec["seed"])
 
 
+def _ssm(heads, vdim, state, groups, conv, norm_groups):
+    return dict(heads=heads, vdim=vdim, state=state, groups=groups, conv=conv, norm_groups=norm_groups)
+
+
+def _sink_latent(heads, dim, rot_dim, vdim, kv_rank, scale, base):
+    return dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, scale=scale,
+                rot=dict(dims=rot_dim, base=base))
+
+
+def _memory(heads, dim, vdim, cap):
+    return dict(heads=heads, dim=dim, vdim=vdim, gate_cap=cap)
+
+
+def _experts(ff, experts, top, identity=0, groups=None, shared=None):
+    router = dict(experts=experts, top=top, identity=identity)
+    if groups is not None:
+        router["groups"] = dict(count=groups[0], keep=groups[1])
+    out = dict(kind="moe", expert=dict(ff=ff), router=router)
+    if shared is not None:
+        out["shared"] = dict(ff=shared)
+    return out
+
+
+def _plain_ff(ff):
+    return dict(kind="dense", ff=ff)
+
+
+# Three tiny Norevik configurations. Between them: state sizes other than the value size, head
+# sizes other than the value size, norm parts other than the key groups, one group and several,
+# one, two and three kept groups, no identity expert, one, and three, a router without groups and
+# without a shared expert, a single chosen expert, layers without a feed-forward, one tap.
+NOREVIK = {
+    "N1": dict(
+        config=dict(architecture="Norevik", vocab=211, width=72, norm=dict(eps=1e-6), embedding=dict(scale=3.0), layers=[
+            dict(type="mamba2", mixer=_ssm(4, 12, 20, 2, 3, 4), mlp=_plain_ff(56)),
+            dict(type="latent_attention", mixer=_sink_latent(3, 12, 6, 10, 20, 0.3, 100.0),
+                 mlp=_experts(24, 5, 2, identity=1, groups=(3, 2), shared=40)),
+            dict(type="mlstm", mixer=_memory(3, 8, 20, 6.0), mlp=_experts(16, 4, 3)),
+            dict(type="mamba2", mixer=_ssm(2, 24, 8, 1, 1, 1), mlp=None),
+            dict(type="latent_attention", mixer=_sink_latent(1, 16, 8, 24, 12, 0.25, 50.0), mlp=None),
+        ]), seed=41, std=0.12),
+    "N2": dict(
+        config=dict(architecture="Norevik", vocab=512, width=256, norm=dict(eps=2e-5), embedding=dict(scale=8.0), layers=[
+            dict(type="mlstm", mixer=_memory(4, 64, 32, 15.0), mlp=_experts(64, 13, 4, identity=3, groups=(4, 3), shared=96)),
+            dict(type="latent_attention", mixer=_sink_latent(4, 64, 32, 64, 96, 0.1, 10000.0), mlp=_plain_ff(384)),
+            dict(type="mamba2", mixer=_ssm(8, 32, 64, 4, 4, 2), mlp=_experts(128, 6, 1, identity=2, groups=(2, 1))),
+            dict(type="mlstm", mixer=_memory(2, 32, 96, 8.0), mlp=None),
+        ]), seed=42, std=0.06),
+    "N3": dict(
+        config=dict(architecture="Norevik", vocab=300, width=64, norm=dict(eps=1e-5), layers=[
+            dict(type="latent_attention", mixer=_sink_latent(2, 8, 4, 12, 16, 0.35, 30.0), mlp=None),
+            dict(type="mlstm", mixer=_memory(1, 16, 16, 10.0), mlp=None),
+            dict(type="mamba2", mixer=_ssm(3, 16, 12, 3, 2, 3), mlp=_experts(32, 3, 2, shared=24)),
+        ]), seed=43, std=0.15),
+}
+
+
+def make_norevik_dir(path, name, dtype=torch.bfloat16, edit=None, steady_routing=False):
+    """A model folder of a tiny Norevik configuration (a name of NOREVIK, or a spec of the caller's
+    own) with seeded random weights; `edit` (a function of the name -> tensor dict) may change them
+    before they are written. The choice of experts is a step function of the router's input: with
+    random weights a runner-up now and then comes within a rounding of bfloat16 activations of the
+    last chosen expert, and the engine and the float64 implementation then choose differently.
+    `steady_routing` is for comparisons in bfloat16: the corrections are 0, 2, 4, ..., so the same
+    experts win for every token (their weights, the scores, still depend on the token) and no
+    comparison rests on a close call. Norm weights are N(1, 0.2); biases, sinks, corrections and the
+    other vectors N(0, 0.5). The state-space mixer's A_log is N(-2, 1) and the matrix memory's
+    forget bias N(2, 1): some heads forget within a few tokens, others carry their state over
+    hundreds."""
+    from llama_rs_metal_b200.engine.model import DecoderModel
+    from llama_rs_metal_b200.registry import find_architecture
+    from llama_rs_metal_b200.runtime import Runtime
+    from llama_rs_metal_b200.weights.random_init import random_tensors, write_model_folder
+    spec = NOREVIK[name] if isinstance(name, str) else name
+    arch = find_architecture(spec["config"])
+    config = arch.config_class.from_dict(spec["config"])
+    model = DecoderModel(arch.plan(config), Runtime(torch.device("cpu"), torch.float32))
+    tensors = random_tensors(model.tensor_specs(), spec["seed"], std=spec["std"], vector_mean=0.0, vector_std=0.5,
+                             dtype=dtype)
+    for name_, t in tensors.items():
+        last = name_.rsplit(".", 1)[-1]
+        if last in ("norm", "norm1", "norm2"):
+            t.mul_(0.4).add_(1.0)
+        elif last == "A_log":
+            t.mul_(2.0).sub_(2.0)
+        elif name_.endswith(".f.b"):
+            t.mul_(2.0).add_(2.0)
+        elif last == "correction" and steady_routing:
+            t.copy_(2.0 * torch.arange(t.numel()))
+    if edit is not None:
+        edit(tensors)
+    return write_model_folder(path, config.to_dict(), tensors, spec["seed"])
+
+
 def random_tokens(seed, length, vocab):
     rng = np.random.default_rng(seed)
     return [int(t) for t in rng.integers(0, vocab, size=length)]

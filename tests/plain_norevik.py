@@ -217,19 +217,20 @@ def feed_forward(h, f, w, p):
 
 
 # --------------------------------------------------------------------------- the model
-def forward(config, w, tokens, layers_out=None):
+def forward(config, w, tokens, layers_out=None, seen=lambda t: t):
     """float64 logits [T, vocab] for one sequence; `layers_out` (a list) receives the residual
-    stream after every layer."""
+    stream after every layer. `seen` is applied to what every sublayer and the head read (the
+    identity; a rounding shows how far a row's logits move when only its inputs are rounded)."""
     eps = config["norm"]["eps"]
     x = w["embed"][torch.tensor(list(tokens), dtype=torch.long)] * config.get("embedding", {}).get("scale", 1.0)
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        y = MIXERS[layer["type"]](x, layer["mixer"], w, p + "mix.", eps)
+        y = MIXERS[layer["type"]](seen(x), layer["mixer"], w, p + "mix.", eps)
         x = x + layer_norm(y, w[p + "norm1"], w[p + "norm1.b"], eps)
         if layer.get("mlp") is not None:
-            y = feed_forward(x, layer["mlp"], w, p + "mlp.")
+            y = feed_forward(seen(x), layer["mlp"], w, p + "mlp.")
             x = x + layer_norm(y, w[p + "norm2"], w[p + "norm2.b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], eps)
-    return x @ w["head"].T
+    return seen(x) @ w["head"].T
