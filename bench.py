@@ -255,11 +255,31 @@ PIBUVIK_SIZES = {   # width, heads, kv heads, feed-forward width, latent width, 
 }
 
 
+def norevik_shape(width, heads, ff, experts, top, layers, vocab=32768):
+    """A Norevik configuration with layers of a real model's widths: a state-space mixer (value
+    heads of 64, state 128), latent attention (head size 96 + 32 rotated, values of 128, a latent of
+    512) and a matrix memory (head size 128) in turn; behind each a mixture of `experts` experts
+    and two identity experts in two groups of which the better one is kept, `top` chosen, and a
+    shared expert as wide as one expert."""
+    moe = dict(kind="moe", expert=dict(ff=ff), shared=dict(ff=ff),
+               router=dict(experts=experts, top=top, identity=2, groups=dict(count=2, keep=1)))
+    kinds = [
+        dict(type="mamba2", mixer=dict(heads=width // 64, vdim=64, state=128, groups=1, conv=4, norm_groups=1), mlp=moe),
+        dict(type="latent_attention", mixer=dict(heads=heads, dim=96, rot_dim=32, vdim=128, kv_rank=512,
+                                                 scale=128 ** -0.5, rot=dict(dims=32, base=10000.0)), mlp=moe),
+        dict(type="mlstm", mixer=dict(heads=heads, dim=128, vdim=128, gate_cap=15.0), mlp=moe),
+    ]
+    return dict(architecture="Norevik", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
+                layers=[dict(kinds[i % 3]) for i in range(layers)])
+
+
 def design_bench(args) -> int:
-    """Prefill and decode throughput of the Kikalix or the Pibuvik design at a few layer sizes, beside
-    the Llama decoder at equal size (the same width, head geometry, vocabulary and number of layer
-    runs; its feed-forward as wide as the experts a token uses, or as the dense one). Random
-    weights, one GPU, bfloat16."""
+    """Prefill and decode throughput of the Kikalix, the Pibuvik or the Norevik design at a few
+    layer sizes, beside an existing decoder at equal size: Kikalix and Pibuvik beside Llama (the same
+    width, head geometry, vocabulary and number of layer runs; its feed-forward as wide as the
+    experts a token uses, or as the dense one), Norevik beside Kikalix, the closest of the designs
+    (state mixers on the same scan, the same experts: equal width, heads, experts, chosen experts,
+    expert width, vocabulary and layer runs). Random weights, one GPU, bfloat16."""
     if args.profile:
         os.environ["LRM_PROFILE"] = "1"
     import numpy as np
@@ -323,7 +343,15 @@ def design_bench(args) -> int:
                 "weight_gb": round(model.weight_bytes / 1e9, 3)}
 
     for size in sizes:
-        if args.design == "pibuvik":
+        twin_name = "llama_equal_size"
+        if args.design == "norevik":
+            width, heads, kv_heads, ff, experts, top, window, layers = DESIGN_SIZES[size]
+            runs, norm_mean = layers + 2, 1.0
+            config = norevik_shape(width, heads, ff, experts, top, runs)
+            twin, twin_name = kikalix_shape(width, heads, kv_heads, ff, experts, top, window, layers), "kikalix_equal_size"
+            shape = dict(width=width, heads=heads, expert_ff=ff, shared_ff=ff, experts=experts, identity=2, top=top,
+                         state_heads=width // 64, state=128, kv_rank=512, layer_runs=runs)
+        elif args.design == "pibuvik":
             width, heads, kv_heads, ff, kv_rank, window, layers = PIBUVIK_SIZES[size]
             config = pibuvik_shape(width, heads, kv_heads, ff, kv_rank, window, layers)
             runs, twin_ff, norm_mean = layers, ff, 1.0
@@ -339,16 +367,19 @@ def design_bench(args) -> int:
         row = {args.design: measure(model, config["vocab"], f"{design_name} {size}")}
         del model
         torch.cuda.empty_cache()
-        twin = llama(width, twin_ff, runs, heads, kv_heads, 128, 8.0, False)
-        twin["vocab_size"] = config["vocab"]
-        model = engine.random(twin, seed=0, std=0.02)
-        row["llama_equal_size"] = measure(model, twin["vocab_size"], f"Llama {size}")
+        if args.design == "norevik":
+            model = engine.random(twin, seed=0, std=0.02, norm_mean=0.0)
+        else:
+            twin = llama(width, twin_ff, runs, heads, kv_heads, 128, 8.0, False)
+            twin["vocab_size"] = config["vocab"]
+            model = engine.random(twin, seed=0, std=0.02)
+        row[twin_name] = measure(model, config["vocab"], f"{twin_name.split('_')[0].capitalize()} {size}")
         del model
         torch.cuda.empty_cache()
         row["shape"] = shape
         out[size] = row
     print(json.dumps({"metric": f"prefill tok/s (one {prompt}-token prompt) and decode tok/s (batch {batch} at "
-                                f"{prompt} tokens), {design_name} beside Llama at equal size",
+                                f"{prompt} tokens), {design_name} beside {'Kikalix' if args.design == 'norevik' else 'Llama'} at equal size",
                       "dtype": "bf16", "data": "synthetic token ids, random-init weights", "n_gpus": 1,
                       "decode_steps": steps, "peaks": peak_source, "cuda_graph": not args.profile, "sizes": out}))
     return 0
@@ -381,9 +412,9 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="time every kernel launch (LRM_PROFILE=1) and print the table to stderr; the "
                              "line's numbers are then those of unfused, uncaptured launches")
-    parser.add_argument("--design", choices=["kikalix", "pibuvik"], default=None,
+    parser.add_argument("--design", choices=["kikalix", "pibuvik", "norevik"], default=None,
                         help="instead of the default workload: prefill and decode throughput of this design at "
-                             "a few layer sizes beside the Llama decoder at equal size (see design_bench)")
+                             "a few layer sizes beside an existing decoder at equal size (see design_bench)")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None,
                         help="with --design: one size only")
     args = parser.parse_args()

@@ -1,6 +1,8 @@
 """A small B200-native inference library for decoders put together from registered parts: the
-Llama 3 dense decoder, the Kikalix decoder (state mixers, windowed attention, experts) and the
-Pibuvik decoder (a gated recurrence, attention with sinks, latent attention, sandwich norms).
+Llama 3 dense decoder, the Kikalix decoder (state mixers, windowed attention, experts), the
+Pibuvik decoder (a gated recurrence, attention with sinks, latent attention, sandwich norms) and the
+Norevik decoder (a state-space mixer, latent attention with sinks, a matrix memory, scored routing
+with identity experts, layer norms behind the sublayers).
 
 Public surface (after crates/llama-rs/src/lib.rs): Engine, Model, Session,
 GenerationOptions, Sampling, GenerationResult, and the typed errors.

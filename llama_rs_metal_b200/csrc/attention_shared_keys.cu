@@ -21,6 +21,8 @@
 // may be cut into splits, a CTA each: a split leaves its rows unnormalized with their maximum and
 // mass ([sequence][head][split][DV + 2] float32) and a second kernel merges the splits in order,
 // out = sum acc_i 2^(m_i - M) / sum l_i 2^(m_i - M).
+// Sinks (one float32 per head, or none): e^sink_h joins the softmax's denominator once, unscaled and
+// without a value; it is added where a row is normalized (here, or in the merge when keys are split).
 // DK a multiple of 16, DV a multiple of 16 up to 512; anything else runs the row-wise kernel.
 #include "attention_mma.cuh"
 
@@ -43,7 +45,10 @@ struct SharedKeysArgs {
   float scale_log2;
   float* partials;                // with n_splits > 1 (one query per sequence): blockIdx.x is the split
   int n_splits;
+  const float* sinks;             // [H], or null
 };
+
+constexpr float kLog2e = 1.4426950408889634f;
 
 template <int PAIRS>  // 16-column blocks of the values one warp accumulates (DV <= 64 * PAIRS)
 __global__ __launch_bounds__(kSkThreads) void attention_shared_keys_kernel(SharedKeysArgs a) {
@@ -255,7 +260,8 @@ __global__ __launch_bounds__(kSkThreads) void attention_shared_keys_kernel(Share
       }
       continue;
     }
-    const float inv = 1.0f / mass;
+    const float sink = (a.sinks != nullptr && head < a.H) ? exp2f(a.sinks[head] * kLog2e - m[half]) : 0.f;
+    const float inv = 1.0f / (mass + sink);
     __nv_bfloat16* dst = a.out + (static_cast<size_t>(start + qi) * a.H + head) * a.DV;
 #pragma unroll
     for (int pi = 0; pi < PAIRS; ++pi) {
@@ -271,7 +277,7 @@ __global__ __launch_bounds__(kSkThreads) void attention_shared_keys_kernel(Share
 
 // One block per (sequence, head): the splits' parts merged in split order.
 __global__ void shared_keys_merge_kernel(const float* __restrict__ partials, __nv_bfloat16* __restrict__ out,
-                                         int n_parts, int DV) {
+                                         int n_parts, int DV, const float* __restrict__ sinks, int H) {
   pdl_trigger();
   pdl_wait();
   const float* src = partials + static_cast<size_t>(blockIdx.x) * n_parts * (DV + 2);
@@ -282,6 +288,7 @@ __global__ void shared_keys_merge_kernel(const float* __restrict__ partials, __n
     const float mi = src[i * (DV + 2) + DV];
     if (mi != -INFINITY) mass = fmaf(src[i * (DV + 2) + DV + 1], exp2f(mi - M), mass);
   }
+  if (sinks != nullptr) mass += exp2f(sinks[blockIdx.x % H] * kLog2e - M);
   for (int d = threadIdx.x; d < DV; d += blockDim.x) {
     float acc = 0.f;
     for (int i = 0; i < n_parts; ++i) {
@@ -306,7 +313,7 @@ int launch_shared_keys(const SharedKeysArgs& a, dim3 grid, cudaStream_t stream) 
   LRM_LAUNCH(kernel, grid, kSkThreads, smem, stream, a);
   if (a.n_splits > 1)
     LRM_LAUNCH(shared_keys_merge_kernel, grid.z * a.H, a.DV >= 256 ? 128 : 64, 0, stream,
-               static_cast<const float*>(a.partials), a.out, a.n_splits, a.DV);
+               static_cast<const float*>(a.partials), a.out, a.n_splits, a.DV, a.sinks, a.H);
   return 0;
 }
 
@@ -323,12 +330,13 @@ LRM_API int lrm_attention_shared_keys_supports(int heads, int dk, int dv, int pa
 // [seqs + 1], kv_lens null. Over the cache: k_pages with page_table / slots, kv_lens [seqs] the
 // lengths after the step; cu_seqlens [seqs + 1] for portions of several queries (at most
 // `max_queries` per sequence), or null for one query per sequence; only then may the keys be cut into
-// `n_splits` > 1 splits, with `partials` holding seqs * heads * n_splits * (dv + 2) floats.
+// `n_splits` > 1 splits, with `partials` holding seqs * heads * n_splits * (dv + 2) floats. `sinks`
+// float32 [heads], or null.
 LRM_API int lrm_attention_shared_keys(const void* q, const void* k_packed, const void* k_pages, void* out,
                                       const int* cu_seqlens, const int* kv_lens, const int* page_table,
                                       int table_stride, const int* slots, int seqs, int max_queries, int heads,
                                       int dk, int dv, float scale, int window, float* partials, int n_splits,
-                                      cudaStream_t stream) {
+                                      const float* sinks, cudaStream_t stream) {
   if (seqs <= 0 || max_queries <= 0) return 0;
   if (!lrm_attention_shared_keys_supports(heads, dk, dv, kTile)) return LRM_UNSUPPORTED;
   if ((k_packed == nullptr) == (k_pages == nullptr)) return LRM_BAD_ARGUMENT;
@@ -338,6 +346,7 @@ LRM_API int lrm_attention_shared_keys(const void* q, const void* k_packed, const
   SharedKeysArgs a;
   a.partials = partials;
   a.n_splits = n_splits > 1 ? n_splits : 1;
+  a.sinks = sinks;
   a.q = static_cast<const __nv_bfloat16*>(q);
   a.k_packed = static_cast<const __nv_bfloat16*>(k_packed);
   a.k_pages = static_cast<const __nv_bfloat16*>(k_pages);
@@ -351,7 +360,7 @@ LRM_API int lrm_attention_shared_keys(const void* q, const void* k_packed, const
   a.DK = dk;
   a.DV = dv;
   a.window = window;
-  a.scale_log2 = scale * 1.4426950408889634f;
+  a.scale_log2 = scale * kLog2e;
   int head_groups = 1;
   if (heads > kRowsPerCta) {
     a.rows_per_query = kRowsPerCta;

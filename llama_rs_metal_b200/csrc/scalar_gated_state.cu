@@ -111,8 +111,13 @@ __global__ void skip_gate_part_norm_kernel(const float* __restrict__ o, const fl
     out[row + c] = from_f32<A>((value(c) * inv) * w[c]);
 }
 
-// One thread per (sequence, head) walks the step's tokens: the running maximum is the only thing
-// that goes from token to token. gates: [T, >= 2H] rows with i~ at column i_off + h, f~ at f_off + h.
+// One warp per (sequence, head). The running maximum m_t = max(f_t + m_(t-1), i_t) is the only thing
+// that goes from token to token, and a run of tokens acts on it as one map m -> max(m + a, b) (a the
+// sum of its f, b what the run makes of minus infinity); two such maps compose into one. Each lane
+// folds a contiguous run of the step's tokens into its (a, b), the lanes' maps are composed by a
+// prefix scan over the warp, and each lane walks its run again from the maximum it now knows. The
+// gates' logarithms rest in `decay` and `take` between the passes.
+// gates: [T, >= 2H] rows with i~ at column i_off + h, f~ at f_off + h.
 template <typename S>
 __global__ void mlstm_gates_kernel(const S* __restrict__ gates, long long stride, int i_off, int f_off,
                                    const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
@@ -121,23 +126,47 @@ __global__ void mlstm_gates_kernel(const S* __restrict__ gates, long long stride
                                    float* __restrict__ take, float* __restrict__ floor, int H) {
   pdl_trigger();
   pdl_wait();
-  const int b = blockIdx.y, h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
-  const int start = cu_seqlens[b], end = cu_seqlens[b + 1], slot = slots[b];
-  float m = slot >= 0 ? top[static_cast<size_t>(slot) * H + h] : 0.f;
+  const int lane = threadIdx.x & 31, b = blockIdx.y, h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (h >= H) return;  // the whole warp
+  const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start, slot = slots[b];
+  const int per = (n + 31) / 32;
+  const int t0 = start + min(n, lane * per), t1 = start + min(n, (lane + 1) * per);
   const float bi = i_bias[h], bf = f_bias[h], under = 1.0f / cap;
-  for (int t = start; t < end; ++t) {
+  float a = 0.f, reach = -INFINITY;
+  for (int t = t0; t < t1; ++t) {
     const S* row = gates + static_cast<size_t>(t) * stride;
     const float ig = cap * tanhf((to_f32(row[i_off + h]) + bi) * under);
     const float fg = -softplus_f(-(cap * tanhf((to_f32(row[f_off + h]) + bf) * under)));
-    const float next = fmaxf(fg + m, ig);
     const size_t at = static_cast<size_t>(t) * H + h;
+    decay[at] = fg;
+    take[at] = ig;
+    a += fg;
+    reach = fmaxf(reach + fg, ig);
+  }
+  // inclusive scan: lane l's map becomes that of the runs of lanes 0 .. l, earlier runs first
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float pa = __shfl_up_sync(0xffffffffu, a, o), pr = __shfl_up_sync(0xffffffffu, reach, o);
+    if (lane >= o) {
+      reach = fmaxf(pr + a, reach);
+      a += pa;
+    }
+  }
+  float before_a = __shfl_up_sync(0xffffffffu, a, 1), before_reach = __shfl_up_sync(0xffffffffu, reach, 1);
+  if (lane == 0) before_a = 0.f, before_reach = -INFINITY;
+  const float carried = slot >= 0 ? top[static_cast<size_t>(slot) * H + h] : 0.f;
+  float m = fmaxf(carried + before_a, before_reach);
+  for (int t = t0; t < t1; ++t) {
+    const size_t at = static_cast<size_t>(t) * H + h;
+    const float fg = decay[at], ig = take[at];
+    const float next = fmaxf(fg + m, ig);
     decay[at] = expf(fg + m - next);
     take[at] = expf(ig - next);
     floor[at] = expf(-next);
     m = next;
   }
-  if (slot >= 0) top[static_cast<size_t>(slot) * H + h] = m;
+  // the last lane ends on the step's last maximum (also when its own run is empty)
+  if (lane == 31 && slot >= 0) top[static_cast<size_t>(slot) * H + h] = m;
 }
 
 // One CTA per (token, head): q times q_scale, k, and v' = take [v | 1 | 0 ..] of dvp columns.
@@ -223,12 +252,13 @@ LRM_API int lrm_mlstm_gates(const void* gates, int dtype, long long stride, int 
                             cudaStream_t stream) {
   if (seqs <= 0) return 0;
   if (H <= 0 || seqs > 65535 || !(cap > 0.f)) return LRM_BAD_ARGUMENT;
-  const dim3 grid((H + 31) / 32, seqs);
+  const int warps = H >= 4 ? 4 : H;
+  const dim3 grid((H + warps - 1) / warps, seqs);
   if (dtype == LRM_F32)
-    LRM_LAUNCH(mlstm_gates_kernel<float>, grid, 32, 0, stream, static_cast<const float*>(gates), stride, i_off, f_off,
+    LRM_LAUNCH(mlstm_gates_kernel<float>, grid, 32 * warps, 0, stream, static_cast<const float*>(gates), stride, i_off, f_off,
                i_bias, f_bias, cap, top, cu_seqlens, slots, decay, take, floor, H);
   else if (dtype == LRM_BF16)
-    LRM_LAUNCH(mlstm_gates_kernel<__nv_bfloat16>, grid, 32, 0, stream, static_cast<const __nv_bfloat16*>(gates), stride,
+    LRM_LAUNCH(mlstm_gates_kernel<__nv_bfloat16>, grid, 32 * warps, 0, stream, static_cast<const __nv_bfloat16*>(gates), stride,
                i_off, f_off, i_bias, f_bias, cap, top, cu_seqlens, slots, decay, take, floor, H);
   else
     return LRM_BAD_ARGUMENT;

@@ -70,9 +70,9 @@ def _value_stride(kv) -> int:
 
 def _shared_keys(q, kv_heads: int, dv: int, slopes, out_scale: float, extras) -> bool:
     """True when the kernel for one key head whose rows hold the values (latent attention's cache
-    layout, csrc/attention_shared_keys.cu) takes this attention."""
+    layout, csrc/attention_shared_keys.cu) takes this attention; it knows sinks, not the temperature."""
     return (not force_rowwise and q.dtype == torch.bfloat16 and kv_heads == 1 and slopes is None
-            and out_scale == 1.0 and extras.plain and q.data_ptr() % 16 == 0
+            and out_scale == 1.0 and extras.temperature is None and q.data_ptr() % 16 == 0
             and bool(library.load().lrm_attention_shared_keys_supports(q.shape[1], q.shape[2], dv, 64)))
 
 
@@ -99,7 +99,7 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
         if shared and dv != d and k.data_ptr() % 16 == 0 and _shared_keys(q, k.shape[1], dv, slopes, out_scale, extras):
             _done(lib.lrm_attention_shared_keys(_ptr(q), _ptr(k), None, _ptr(out), _ptr(cu_seqlens), None, None, 0,
                                                 None, cu_seqlens.numel() - 1, max_seq_len, Hq, d, dv,
-                                                ctypes.c_float(scale), window, None, 1, _stream()),
+                                                ctypes.c_float(scale), window, None, 1, _ptr(extras.sinks), _stream()),
                   "attention_shared_keys")
             return
         if dv == d and _tiled(q, 64) and shared:
@@ -191,7 +191,8 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
         partials = torch.empty((B, Hq, splits, dv + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
         _done(lib.lrm_attention_shared_keys(_ptr(q), None, _ptr(kv.k), _ptr(out), None, _ptr(kv_lens),
                                             _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots), B, 1, Hq, d,
-                                            dv, ctypes.c_float(scale), window, _ptr(partials), splits, _stream()),
+                                            dv, ctypes.c_float(scale), window, _ptr(partials), splits, _ptr(extras.sinks),
+                                            _stream()),
               "attention_shared_keys", launches=2 if splits > 1 else 1)
         return
     if dv == d and _tiled(q, kv.page_size):
@@ -226,7 +227,7 @@ def extend(q, kv, out, cu_seqlens, seq_of_token, positions, slots, kv_lens, max_
         _done(lib.lrm_attention_shared_keys(_ptr(q), None, _ptr(kv.k), _ptr(out), _ptr(cu_seqlens), _ptr(kv_lens),
                                             _ptr(kv.page_table), kv.page_table.shape[1], _ptr(slots),
                                             cu_seqlens.numel() - 1, max_seq_len, Hq, d, dv, ctypes.c_float(scale),
-                                            window, None, 1, _stream()),
+                                            window, None, 1, _ptr(extras.sinks), _stream()),
               "attention_shared_keys")
         return
     if dv == d and _tiled(q, kv.page_size):

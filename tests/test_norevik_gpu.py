@@ -344,3 +344,77 @@ def test_replay_through_the_trace_runner(folders, plain, dtype, tmp_path):
         rows = trace.rows[step]
         ref = Ref.stack([refs[rid.split(":")[-1]][pos] for rid, pos in rows])
         close(outputs[step], ref, dtype, f"step {step}")
+
+
+# --------------------------------------------------------------------------- configurations drawn at random
+def drawn_configuration(seed):
+    rng = np.random.default_rng(seed)
+
+    def pick(*values):
+        return values[int(rng.integers(len(values)))]
+
+    def feed_forward():
+        kind = pick(None, "dense", "moe", "moe")
+        if kind is None:
+            return None
+        if kind == "dense":
+            return helpers._plain_ff(int(pick(24, 64, 100)))
+        count = int(pick(1, 2, 3))
+        size = int(pick(1, 2, 4))                       # outputs per group
+        outputs = count * size
+        identity = int(rng.integers(0, min(3, outputs)))
+        keep = int(rng.integers(1, count + 1))
+        top = int(rng.integers(1, keep * size + 1))
+        return helpers._experts(int(pick(8, 24, 40)), outputs - identity, top, identity=identity,
+                                groups=(count, keep) if rng.integers(3) else None, shared=pick(None, 16, 48))
+    width = int(pick(40, 64, 88, 136))
+    layers = []
+    for _ in range(int(rng.integers(2, 6))):
+        kind = pick("mamba2", "latent_attention", "mlstm")
+        if kind == "mamba2":
+            groups = int(pick(1, 2, 3))
+            heads, vdim = groups * int(pick(1, 2)), int(pick(4, 8, 20, 64))
+            parts = [p for p in (1, 2, 3, 4, 5) if (heads * vdim) % p == 0]
+            mixer = helpers._ssm(heads, vdim, int(pick(4, 16, 24, 64, 128)), groups, int(pick(1, 2, 4, 5)), int(pick(*parts)))
+        elif kind == "latent_attention":
+            mixer = helpers._sink_latent(int(pick(1, 2, 5)), int(pick(4, 16, 24)), int(pick(2, 8, 16)), int(pick(8, 12, 32)),
+                                         int(pick(8, 24, 40)), float(pick(0.1, 0.4)), float(pick(30.0, 10000.0)))
+        else:
+            mixer = helpers._memory(int(pick(1, 2, 3)), int(pick(4, 16, 40)), int(pick(3, 8, 16, 63)), float(pick(2.0, 10.0, 30.0)))
+        layers.append(dict(type=kind, mixer=mixer, mlp=feed_forward()))
+    config = dict(architecture="Norevik", vocab=int(pick(97, 256, 333)), width=width, norm=dict(eps=float(pick(1e-6, 1e-4))),
+                  embedding=dict(scale=float(pick(0.5, 1.0, 6.0))), layers=layers)
+    return dict(config=config, seed=2000 + seed, std=float(pick(0.08, 0.15)))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(engine, tmp_path, seed):
+    """Other sizes, orders of layers and constants than the fixed configurations: a prompt whole,
+    then tokens one by one, a second sequence beside it in portions."""
+    spec = drawn_configuration(seed)
+    for dtype in ("float32", "bfloat16"):
+        folder = helpers.make_norevik_dir(str(tmp_path / dtype), spec, steady_routing=dtype == "bfloat16")
+        plain = {("drawn", dtype): P.read_model(folder)}
+        V = spec["config"]["vocab"]
+        a, b = helpers.random_tokens(seed, 150, V), helpers.random_tokens(seed + 50, 100, V)
+        ref_a, ref_b = reference(plain, ("drawn", dtype), a), reference(plain, ("drawn", dtype), b)
+        _REFS.pop((("drawn", dtype), tuple(a)))          # the next seed's folder is another model
+        _REFS.pop((("drawn", dtype), tuple(b)))
+        runner, cache, _ = open_runner(engine, folder, dtype)
+        sa, sb = cache.open_slot(), cache.open_slot()
+        out = runner.step([entry(sa, a[:120]), entry(sb, b[:3])]).cpu().numpy()
+        close(out[:120], ref_a[:120], dtype, f"seed {seed}: prompt a", factor=2.0)
+        close(out[120:], ref_b[:3], dtype, f"seed {seed}: prompt b", factor=2.0)
+        out = runner.step([entry(sa, a[120:121]), entry(sb, b[3:70])]).cpu().numpy()     # one token and a portion
+        close(out[:1], ref_a[120:121], dtype, f"seed {seed}: a's next token", factor=2.0)
+        close(out[1:], ref_b[3:70], dtype, f"seed {seed}: b's portion", factor=2.0)
+        rows_a, rows_b = [], []
+        for t in range(121, 150):
+            entries = [entry(sa, [a[t]])] + ([entry(sb, [b[t - 51]])] if t - 51 < 100 else [])
+            out = runner.step(entries).cpu().numpy()
+            rows_a.append(out[0])
+            if len(entries) > 1:
+                rows_b.append(out[1])
+        close(np.stack(rows_a), ref_a[121:], dtype, f"seed {seed}: a decoded", factor=2.0)
+        close(np.stack(rows_b), ref_b[70:70 + len(rows_b)], dtype, f"seed {seed}: b decoded", factor=2.0)
+        runner.check_device_status()

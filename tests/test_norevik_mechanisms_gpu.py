@@ -135,6 +135,31 @@ def test_a_far_key_wins_and_a_sink_takes_its_share(engine, tmp_path, far_at):
         runner.check_device_status()
 
 
+@pytest.mark.parametrize("splits", [1, 3, 7])
+def test_the_sink_counts_once_however_a_decode_steps_keys_are_cut(engine, tmp_path, splits):
+    """Decoding over 300 cached tokens with the key tiles of a sequence cut into splits that are merged
+    afterwards: the sink joins the denominator once, in the merge, not once per split."""
+    from llama_rs_metal_b200.kernels import attention_dispatch
+    spec = one_layer("latent_attention", helpers._sink_latent(3, 16, 16, 32, 48, 0.2, 100.0), seed=76)
+
+    def edit(t):
+        t["l0.mix.sink"].copy_(torch.tensor([3.0, -1.0, 6.0]))
+    folder = helpers.make_norevik_dir(str(tmp_path / "cut"), spec, edit=edit)
+    config, tensors = P.read_model(folder)
+    a, b = helpers.random_tokens(10, 330, 97), helpers.random_tokens(11, 90, 97)
+    ref_a, ref_b = P.forward(config, tensors, a).numpy(), P.forward(config, tensors, b).numpy()
+    runner, cache, _ = open_runner(engine, folder, "bfloat16", use_graphs=False)
+    sa, sb = cache.open_slot(), cache.open_slot()
+    runner.step([entry(sa, a[:300], []), entry(sb, b[:60], [])])
+    attention_dispatch.force_shared_key_splits = splits
+    try:
+        outs = [runner.step([entry(sa, [a[300 + t]]), entry(sb, [b[60 + t]])]).cpu().numpy() for t in range(30)]
+    finally:
+        attention_dispatch.force_shared_key_splits = None
+    close(np.stack([o[0] for o in outs]), ref_a[300:], "bfloat16", "the long sequence", strict=True)
+    close(np.stack([o[1] for o in outs]), ref_b[60:], "bfloat16", "the short sequence", strict=True)
+
+
 def test_rotation_pairs_neighbours_and_counts_from_each_sequences_start(engine, tmp_path):
     """Only the rotated parts carry the scores (the unrotated query is zero), with a base so small
     that every frequency turns many times over the prompt: pairing other dimensions, another angle
