@@ -326,6 +326,14 @@ LRM_API int lrm_attention_shared_keys_supports(int heads, int dk, int dv, int pa
              : 0;
 }
 
+// CTAs of this kernel that fit on one SM at key width dk (their shared memory decides): what a caller
+// that cuts a decode step's keys into splits fills the SMs with once.
+LRM_API int lrm_attention_shared_keys_ctas_per_sm(int dk) {
+  const size_t bytes = shared_keys_smem(dk) + 1024;  // the driver's own share of a CTA's shared memory
+  const int fit = static_cast<int>((227 * 1024) / bytes);
+  return fit < 1 ? 1 : (fit > 4 ? 4 : fit);
+}
+
 // q [queries, heads, dk], out [queries, heads * dv], bfloat16. A prompt: k_packed [queries, dk], cu_seqlens
 // [seqs + 1], kv_lens null. Over the cache: k_pages with page_table / slots, kv_lens [seqs] the
 // lengths after the step; cu_seqlens [seqs + 1] for portions of several queries (at most

@@ -133,6 +133,7 @@ __global__ void mlstm_gates_kernel(const S* __restrict__ gates, long long stride
   const int t0 = start + min(n, lane * per), t1 = start + min(n, (lane + 1) * per);
   const float bi = i_bias[h], bf = f_bias[h], under = 1.0f / cap;
   float a = 0.f, reach = -INFINITY;
+#pragma unroll 4  // the loads of a run's rows lie far apart: several in flight
   for (int t = t0; t < t1; ++t) {
     const S* row = gates + static_cast<size_t>(t) * stride;
     const float ig = cap * tanhf((to_f32(row[i_off + h]) + bi) * under);

@@ -183,9 +183,12 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
     lib = library.load()
     if (getattr(kv, "values_in_keys", False) and dv != d and kv.page_size == 64
             and _shared_keys(q, kv.kv_heads, dv, slopes, out_scale, extras)):
-        # few CTAs (sequences x groups of 32 heads): the key tiles are cut until about two CTAs per SM run
+        # few CTAs (sequences x groups of 32 heads): the key tiles are cut until the SMs are filled once
+        # with as many CTAs as their shared memory lets run side by side (two at key width 288, one at
+        # 544); more splits than that only add a second round of CTAs and partial rows for the merge
         keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
-        splits = max(1, min(-(-keys // 64), 2 * SM_COUNT // (B * -(-Hq // 32))))
+        room = int(lib.lrm_attention_shared_keys_ctas_per_sm(d)) * SM_COUNT
+        splits = max(1, min(-(-keys // 64), room // (B * -(-Hq // 32))))
         if force_shared_key_splits is not None:
             splits = force_shared_key_splits
         partials = torch.empty((B, Hq, splits, dv + 2), dtype=torch.float32, device=q.device) if splits > 1 else None
