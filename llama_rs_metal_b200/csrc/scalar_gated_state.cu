@@ -111,29 +111,46 @@ __global__ void skip_gate_part_norm_kernel(const float* __restrict__ o, const fl
     out[row + c] = from_f32<A>((value(c) * inv) * w[c]);
 }
 
-// One warp per (sequence, head). The running maximum m_t = max(f_t + m_(t-1), i_t) is the only thing
+// One CTA per (sequence, head). The running maximum m_t = max(f_t + m_(t-1), i_t) is the only thing
 // that goes from token to token, and a run of tokens acts on it as one map m -> max(m + a, b) (a the
-// sum of its f, b what the run makes of minus infinity); two such maps compose into one. Each lane
-// folds a contiguous run of the step's tokens into its (a, b), the lanes' maps are composed by a
-// prefix scan over the warp, and each lane walks its run again from the maximum it now knows. The
-// gates' logarithms rest in `decay` and `take` between the passes.
+// sum of its f, b what the run makes of minus infinity); two such maps compose into one, and the map
+// (0, -inf) changes nothing. Each thread folds a contiguous run of the step's tokens (one or two
+// tokens of a long prompt) into its (a, b); the threads' maps are composed by a prefix scan over each
+// warp and then over the warps' totals; each thread walks its run again from the maximum it now
+// knows. The gates' logarithms rest in `decay` and `take` between the passes.
 // gates: [T, >= 2H] rows with i~ at column i_off + h, f~ at f_off + h.
+struct MaxMap {
+  float a, reach;
+};
+__device__ __forceinline__ MaxMap then(MaxMap first, MaxMap second) {
+  return MaxMap{first.a + second.a, fmaxf(first.reach + second.a, second.reach)};
+}
+// lane l ends with the composition of lanes 0 .. l, earlier lanes first
+__device__ __forceinline__ MaxMap warp_prefix(MaxMap mine, int lane) {
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const MaxMap before{__shfl_up_sync(0xffffffffu, mine.a, o), __shfl_up_sync(0xffffffffu, mine.reach, o)};
+    if (lane >= o) mine = then(before, mine);
+  }
+  return mine;
+}
+
 template <typename S>
 __global__ void mlstm_gates_kernel(const S* __restrict__ gates, long long stride, int i_off, int f_off,
                                    const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
                                    float* __restrict__ top, const int* __restrict__ cu_seqlens,
                                    const int* __restrict__ slots, float* __restrict__ decay,
                                    float* __restrict__ take, float* __restrict__ floor, int H) {
+  __shared__ MaxMap totals[32];
   pdl_trigger();
   pdl_wait();
-  const int lane = threadIdx.x & 31, b = blockIdx.y, h = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (h >= H) return;  // the whole warp
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int h = blockIdx.x, b = blockIdx.y;
   const int start = cu_seqlens[b], n = cu_seqlens[b + 1] - start, slot = slots[b];
-  const int per = (n + 31) / 32;
-  const int t0 = start + min(n, lane * per), t1 = start + min(n, (lane + 1) * per);
+  const int per = (n + blockDim.x - 1) / blockDim.x;
+  const int t0 = start + min(n, static_cast<int>(threadIdx.x) * per), t1 = start + min(n, (static_cast<int>(threadIdx.x) + 1) * per);
   const float bi = i_bias[h], bf = f_bias[h], under = 1.0f / cap;
-  float a = 0.f, reach = -INFINITY;
-#pragma unroll 4  // the loads of a run's rows lie far apart: several in flight
+  MaxMap mine{0.f, -INFINITY};
   for (int t = t0; t < t1; ++t) {
     const S* row = gates + static_cast<size_t>(t) * stride;
     const float ig = cap * tanhf((to_f32(row[i_off + h]) + bi) * under);
@@ -141,22 +158,21 @@ __global__ void mlstm_gates_kernel(const S* __restrict__ gates, long long stride
     const size_t at = static_cast<size_t>(t) * H + h;
     decay[at] = fg;
     take[at] = ig;
-    a += fg;
-    reach = fmaxf(reach + fg, ig);
+    mine = then(mine, MaxMap{fg, ig});
   }
-  // inclusive scan: lane l's map becomes that of the runs of lanes 0 .. l, earlier runs first
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const float pa = __shfl_up_sync(0xffffffffu, a, o), pr = __shfl_up_sync(0xffffffffu, reach, o);
-    if (lane >= o) {
-      reach = fmaxf(pr + a, reach);
-      a += pa;
-    }
+  const MaxMap through = warp_prefix(mine, lane);  // this warp's runs up to and with this lane's
+  if (lane == 31) totals[warp] = through;
+  __syncthreads();
+  if (warp == 0) {
+    const MaxMap whole = warp_prefix(lane < warps ? totals[lane] : MaxMap{0.f, -INFINITY}, lane);
+    totals[lane] = whole;  // warps 0 .. lane
   }
-  float before_a = __shfl_up_sync(0xffffffffu, a, 1), before_reach = __shfl_up_sync(0xffffffffu, reach, 1);
-  if (lane == 0) before_a = 0.f, before_reach = -INFINITY;
+  __syncthreads();
+  MaxMap before{__shfl_up_sync(0xffffffffu, through.a, 1), __shfl_up_sync(0xffffffffu, through.reach, 1)};
+  if (lane == 0) before = MaxMap{0.f, -INFINITY};
+  if (warp > 0) before = then(totals[warp - 1], before);
   const float carried = slot >= 0 ? top[static_cast<size_t>(slot) * H + h] : 0.f;
-  float m = fmaxf(carried + before_a, before_reach);
+  float m = fmaxf(carried + before.a, before.reach);
   for (int t = t0; t < t1; ++t) {
     const size_t at = static_cast<size_t>(t) * H + h;
     const float fg = decay[at], ig = take[at];
@@ -166,8 +182,8 @@ __global__ void mlstm_gates_kernel(const S* __restrict__ gates, long long stride
     floor[at] = expf(-next);
     m = next;
   }
-  // the last lane ends on the step's last maximum (also when its own run is empty)
-  if (lane == 31 && slot >= 0) top[static_cast<size_t>(slot) * H + h] = m;
+  // the last thread ends on the step's last maximum (also when its own run is empty)
+  if (threadIdx.x == blockDim.x - 1 && slot >= 0) top[static_cast<size_t>(slot) * H + h] = m;
 }
 
 // One CTA per (token, head): q times q_scale, k, and v' = take [v | 1 | 0 ..] of dvp columns.
@@ -246,20 +262,23 @@ LRM_API int lrm_skip_gate_part_norm(const float* o, const float* x, const float*
 }
 
 // gates [T, stride]: i~ at column i_off + h, f~ at f_off + h. top float32 [slots, H] (the running
-// maximum, carried). -> decay, take, floor float32 [T, H].
+// maximum, carried). -> decay, take, floor float32 [T, H]. max_tokens: no sequence brings more tokens
+// than this to the step (it only sizes the CTAs).
 LRM_API int lrm_mlstm_gates(const void* gates, int dtype, long long stride, int i_off, int f_off,
                             const float* i_bias, const float* f_bias, float cap, float* top, const int* cu_seqlens,
                             const int* slots, float* decay, float* take, float* floor, int seqs, int H,
-                            cudaStream_t stream) {
+                            int max_tokens, cudaStream_t stream) {
   if (seqs <= 0) return 0;
-  if (H <= 0 || seqs > 65535 || !(cap > 0.f)) return LRM_BAD_ARGUMENT;
-  const int warps = H >= 4 ? 4 : H;
-  const dim3 grid((H + warps - 1) / warps, seqs);
+  if (H <= 0 || seqs > 65535 || !(cap > 0.f) || max_tokens <= 0) return LRM_BAD_ARGUMENT;
+  // as many threads as the longest sequence can have tokens, in whole warps, up to 1024
+  int threads = 32;
+  while (threads < max_tokens && threads < 1024) threads *= 2;
+  const dim3 grid(H, seqs);
   if (dtype == LRM_F32)
-    LRM_LAUNCH(mlstm_gates_kernel<float>, grid, 32 * warps, 0, stream, static_cast<const float*>(gates), stride, i_off, f_off,
+    LRM_LAUNCH(mlstm_gates_kernel<float>, grid, threads, 0, stream, static_cast<const float*>(gates), stride, i_off, f_off,
                i_bias, f_bias, cap, top, cu_seqlens, slots, decay, take, floor, H);
   else if (dtype == LRM_BF16)
-    LRM_LAUNCH(mlstm_gates_kernel<__nv_bfloat16>, grid, 32 * warps, 0, stream, static_cast<const __nv_bfloat16*>(gates), stride,
+    LRM_LAUNCH(mlstm_gates_kernel<__nv_bfloat16>, grid, threads, 0, stream, static_cast<const __nv_bfloat16*>(gates), stride,
                i_off, f_off, i_bias, f_bias, cap, top, cu_seqlens, slots, decay, take, floor, H);
   else
     return LRM_BAD_ARGUMENT;

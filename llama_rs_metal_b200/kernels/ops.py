@@ -663,7 +663,7 @@ def capped_gates(gates: torch.Tensor, i_column: int, f_column: int, i_bias: torc
     _done(_lib().lrm_mlstm_gates(_ptr(gates), _code(gates.dtype), ctypes.c_longlong(gates.shape[1]), i_column,
                                  f_column, _ptr(i_bias), _ptr(f_bias), ctypes.c_float(cap), _ptr(top),
                                  _ptr(cu_seqlens), _ptr(slots), _ptr(decay), _ptr(take), _ptr(floor), slots.numel(), H,
-                                 _stream()), "capped_gates")
+                                 T, _stream()), "capped_gates")
     return decay, take, floor
 
 
