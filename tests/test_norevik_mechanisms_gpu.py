@@ -9,7 +9,7 @@ import torch
 
 import helpers
 import plain_norevik as P
-from test_norevik_gpu import close, entry, open_runner
+from test_norevik_gpu import close, entry, open_runner, reference
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -302,3 +302,29 @@ def test_layer_norm_and_the_norm_behind_a_sublayer(width):
         assert (s.cpu().to(F64) - expect).abs().max() < 2e-5 * expect.abs().max()
         if cast_dtype is not None:
             assert torch.equal(out, s.to(cast_dtype)), "the rounded copy is the rounding of the updated stream"
+
+
+# --------------------------------------------------------------------------- awkward sizes
+def test_sizes_that_are_multiples_of_nothing(engine, tmp_path):
+    """Width 67, vocabulary 101, head, state, value, latent and expert sizes that are odd or prime: no
+    size is a multiple of 4, 8 or 16, so every kernel's path for unaligned rows runs (and the
+    vectorized or tensor-core path of none)."""
+    spec = dict(config=dict(architecture="Norevik", vocab=101, width=67, norm=dict(eps=3e-6), embedding=dict(scale=2.5), layers=[
+        dict(type="mamba2", mixer=helpers._ssm(3, 5, 7, 3, 3, 5), mlp=helpers._experts(9, 3, 2, identity=1, groups=(2, 2), shared=11)),
+        dict(type="latent_attention", mixer=helpers._sink_latent(3, 5, 6, 7, 9, 0.3, 77.0), mlp=helpers._plain_ff(13)),
+        dict(type="mlstm", mixer=helpers._memory(5, 3, 9, 3.5), mlp=None),
+    ]), seed=77, std=0.2)
+    for dtype in ("float32", "bfloat16"):
+        folder = helpers.make_norevik_dir(str(tmp_path / dtype), spec, steady_routing=dtype == "bfloat16")
+        plain = {("odd", dtype): P.read_model(folder)}
+        a, b = helpers.random_tokens(12, 120, 101), helpers.random_tokens(13, 45, 101)
+        ref_a, ref_b = reference(plain, ("odd", dtype), a), reference(plain, ("odd", dtype), b)   # with each row's allowance
+        runner, cache, _ = open_runner(engine, folder, dtype)
+        sa, sb = cache.open_slot(), cache.open_slot()
+        out = runner.step([entry(sa, a[:100]), entry(sb, b[:25])]).cpu().numpy()
+        close(out[:100], ref_a[:100], dtype, "the first prompt")
+        close(out[100:], ref_b[:25], dtype, "the second prompt")
+        outs = [runner.step([entry(sa, [a[100 + t]]), entry(sb, [b[25 + t]])]).cpu().numpy() for t in range(20)]
+        close(np.stack([o[0] for o in outs]), ref_a[100:], dtype, "the first sequence, decoded")
+        close(np.stack([o[1] for o in outs]), ref_b[25:], dtype, "the second sequence, decoded")
+        runner.check_device_status()
