@@ -185,7 +185,7 @@ def decode(q, kv, out, slots, kv_lens, max_kv_len: int, scale: float, window: in
             and _shared_keys(q, kv.kv_heads, dv, slopes, out_scale, extras)):
         # few CTAs (sequences x groups of 32 heads): the key tiles are cut until the SMs are filled once
         # with as many CTAs as their shared memory lets run side by side (two at key width 288, one at
-        # 544); more splits than that only add a second round of CTAs and partial rows for the merge
+        # 544); more splits than that only add a second wave of CTAs and partial rows for the merge
         keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
         room = int(lib.lrm_attention_shared_keys_ctas_per_sm(d)) * SM_COUNT
         splits = max(1, min(-(-keys // 64), room // (B * -(-Hq // 32))))

@@ -219,15 +219,15 @@ def test_a_prompt_geometry_that_comes_again_is_captured_and_replayed(engine, fol
     runner, cache, _ = open_runner(engine, folders[name, dtype], dtype)
     V = vocab_of(name)
     following, expected = [], []
-    for round_ in range(4):
-        seqs = [helpers.random_tokens(500 + 10 * round_ + i, n, V) for i, n in enumerate([70, 3, 41])]
+    for turn in range(4):
+        seqs = [helpers.random_tokens(500 + 10 * turn + i, n, V) for i, n in enumerate([70, 3, 41])]
         slots = [cache.open_slot() for _ in seqs]
         out = runner.step([entry(sl, s) for sl, s in zip(slots, seqs)]).cpu().numpy()
         row = 0
         for s in seqs:
-            close(out[row:row + len(s)], reference(plain, (name, dtype), s), dtype, f"{name} round {round_}")
+            close(out[row:row + len(s)], reference(plain, (name, dtype), s), dtype, f"{name} turn {turn}")
             row += len(s)
-        nxt = [int(t) for t in helpers.random_tokens(900 + round_, len(seqs), V)]
+        nxt = [int(t) for t in helpers.random_tokens(900 + turn, len(seqs), V)]
         out = runner.step([entry(sl, [t]) for sl, t in zip(slots, nxt)]).cpu().numpy()
         for i, (s, t) in enumerate(zip(seqs, nxt)):
             following.append(out[i])
