@@ -299,9 +299,12 @@ LRM_API int lrm_rms_norm(float* x, const void* w, int w_dtype, void* out, int ou
 // sublayer's float32 output and `stream` the float32 residual stream, updated in place. With a
 // second weight `w2` the updated row is normalized once more in the same pass (the norm in front
 // of the next sublayer): out2[t] = stream[t] / sqrt(mean(stream[t]^2) + eps2) * w2. A thread
-// keeps its PER elements of the row in registers between the passes.
+// keeps its PER elements of the row in registers between the passes. `stream` and `y` are plain
+// pointers: a load through a `const __restrict__` pointer counts as invariant for the whole kernel
+// and may be moved ahead of griddepcontrol.wait, next to the weight loads that stand there on
+// purpose, while the kernel before this one is still writing y.
 template <typename W, typename O, int PER>
-__global__ void rms_norm_add_kernel(float* __restrict__ stream, const float* __restrict__ y,
+__global__ void rms_norm_add_kernel(float* stream, const float* y,
                                     const W* __restrict__ w, float mult, float eps, const W* __restrict__ w2,
                                     O* __restrict__ out2, float eps2, int hidden) {
   __shared__ float scratch[32];
@@ -347,7 +350,7 @@ __global__ void rms_norm_add_kernel(float* __restrict__ stream, const float* __r
 // The same with 16-byte accesses (hidden % 4 == 0, 16-byte aligned rows): a thread keeps PER4 groups
 // of four consecutive elements.
 template <typename W, typename O, int PER4>
-__global__ void rms_norm_add_vec_kernel(float* __restrict__ stream, const float* __restrict__ y,
+__global__ void rms_norm_add_vec_kernel(float* stream, const float* y,
                                         const W* __restrict__ w, float mult, float eps, const W* __restrict__ w2,
                                         O* __restrict__ out2, float eps2, int hidden) {
   __shared__ float scratch[32];
