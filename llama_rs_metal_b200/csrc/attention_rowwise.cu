@@ -10,7 +10,8 @@
 // chunks of any size do the same arithmetic in the same order. The paged entry
 // takes any number of queries per sequence (a decoded token, or a portion of
 // several tokens appended to a started sequence, whose own keys are already in
-// the cache). A window w lets a query at position p see keys p-w+1 .. p.
+// the cache). A window w lets a query at position p see keys p-w+1 .. p; a negative w stands for
+// chunks of -w positions (first_visible_key).
 // Values may have another width than keys (dv against d). With `slopes` (one
 // float32 per query head) a key at distance n = p - j behind the query loses
 // slope_h * n from its score (a linear distance penalty, no rotation needed);
@@ -112,7 +113,7 @@ __global__ void attention_packed_kernel(const A* __restrict__ q, const A* __rest
   const int t = blockIdx.x, h = blockIdx.y;
   const int start = cu_seqlens[seq_of_token[t]];
   const int pos = t - start;
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first = first_visible_key(pos, window);
   PackedKeys keys{k, v, static_cast<size_t>(start), kv_heads, d, v_stride};
   const size_t row = static_cast<size_t>(t) * q_heads + h;
   attend_row<A, PER>(q + row * d, out + row * dv, keys, h / (q_heads / kv_heads), first, pos, d, dv,
@@ -137,7 +138,7 @@ __global__ void attention_paged_kernel(const A* __restrict__ q, const A* __restr
   const int t = blockIdx.x, h = blockIdx.y;
   const int b = seq_of_token != nullptr ? seq_of_token[t] : t;
   const int pos = positions != nullptr ? positions[t] : kv_lens[b] - 1;
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int first = first_visible_key(pos, window);
   PagedKeys keys{k_pages, v_pages, page_table + static_cast<size_t>(slots[b]) * table_stride,
                  kv_heads, d, v_stride, page_size};
   const size_t row = static_cast<size_t>(t) * q_heads + h;

@@ -77,7 +77,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
   const float scale_row[2] = {scale_log2 * query_temperature(row0 + g, temp_coef, temp_every),
                               scale_log2 * query_temperature(row0 + g + 8, temp_coef, temp_every)};
 
-  const int kt_first = window > 0 ? max(0, q0 - window + 1) / kTile : 0;
+  const int kt_first = first_visible_key(q0, window) / kTile;
   const int kt_last = qt;
   const size_t kv_pitch = static_cast<size_t>(kv_heads) * D;
   auto issue = [&](int kt, int stage) {
@@ -108,7 +108,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
       for (int e = 0; e < 4; ++e) {
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = row0 + g + 8 * (e >> 1);
-        const bool visible = key <= query && (window <= 0 || key > query - window);
+        const bool visible = key <= query && key >= first_visible_key(query, window);
         s[nt][e] = visible ? s[nt][e] * scale_row[e >> 1] - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }
@@ -178,7 +178,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
                               scale_log2 * query_temperature(before + row0 + g + 8, temp_coef, temp_every)};
 
   // keys the tile's queries see: from the first query's window to the last query's own position
-  const int first_key = window > 0 ? max(0, before + q0 - window + 1) : 0;
+  const int first_key = first_visible_key(before + q0, window);
   const int kt_first = first_key / kTile;
   const int kt_last = (before + min(q0 + kTile, n) - 1) / kTile;
   auto issue = [&](int kt, int stage) {
@@ -213,7 +213,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
       for (int e = 0; e < 4; ++e) {
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = before + row0 + g + 8 * (e >> 1);  // position in the sequence
-        const bool visible = key <= query && (window <= 0 || key > query - window);
+        const bool visible = key <= query && key >= first_visible_key(query, window);
         s[nt][e] = visible ? s[nt][e] * scale_row[e >> 1] - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }
@@ -270,7 +270,7 @@ __global__ __launch_bounds__(kThreads) void attention_decode_tiled_kernel(
     if (g < rows) slope_log2[0] = slopes[head0 + g] * 1.4426950408889634f;
     if (g + 8 < rows) slope_log2[1] = slopes[head0 + g + 8] * 1.4426950408889634f;
   }
-  const int first_key = window > 0 ? max(0, len - window) : 0;
+  const int first_key = len > 0 ? first_visible_key(len - 1, window) : 0;
   const int page_first = first_key / kTile, page_end = (len + kTile - 1) / kTile;
   const int n_pages = page_end - page_first;
   const int per_split = (n_pages + n_splits - 1) / n_splits;

@@ -54,6 +54,14 @@ inline cudaError_t lrm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     if (e__ != cudaSuccess) return static_cast<int>(e__);                                   \
   } while (0)
 
+// Which keys a query sees, as one number. window > 0: the query at position p sees keys
+// p - window + 1 .. p (a sliding window). window < 0: positions form chunks of -window counted from
+// position 0 of the sequence, and a query sees the keys of its own chunk up to itself. 0: every key
+// up to itself. The first visible key never moves back as p grows, in all three cases.
+__device__ __forceinline__ int first_visible_key(int pos, int window) {
+  return window > 0 ? max(0, pos - window + 1) : window < 0 ? pos - pos % (-window) : 0;
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -248,3 +248,70 @@ LRM_API int lrm_cast(const void* src, int src_dtype, void* dst, int dst_dtype, l
   return 0;
 }
 
+
+// The tanh form of GELU as a gate: out = gelu(gate) * up with gelu(z) = 0.5 z (1 + tanh(sqrt(2/pi)
+// (z + 0.044715 z^3))), from the gate/up column layout of silu_mul. The input may be float32 while
+// the output has the activation type (a product that keeps its sums until the activation).
+template <typename S, typename A>
+__global__ void gelu_tanh_mul_kernel(const S* gate_up, A* __restrict__ out, size_t total, int inter, int block) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / inter;
+  const int c = static_cast<int>(idx % inter);
+  const size_t base = t * 2 * inter + static_cast<size_t>(c / block) * 2 * block + c % block;
+  const float g = to_f32(gate_up[base]), u = to_f32(gate_up[base + block]);
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+  out[idx] = from_f32<A>(0.5f * g * (1.0f + tanhf(inner)) * u);
+}
+
+LRM_API int lrm_gelu_tanh_mul(const void* gate_up, int in_dtype, void* out, int out_dtype, long long rows, int inter,
+                              int block, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (inter <= 0 || block <= 0 || inter % block != 0) return LRM_BAD_ARGUMENT;
+  const size_t total = static_cast<size_t>(rows) * inter;
+  if (in_dtype == LRM_F32 && out_dtype == LRM_F32)
+    LRM_LAUNCH((gelu_tanh_mul_kernel<float, float>), blocks_for(total), 256, 0, stream,
+               static_cast<const float*>(gate_up), static_cast<float*>(out), total, inter, block);
+  else if (in_dtype == LRM_F32 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((gelu_tanh_mul_kernel<float, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const float*>(gate_up), static_cast<__nv_bfloat16*>(out), total, inter, block);
+  else if (in_dtype == LRM_BF16 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((gelu_tanh_mul_kernel<__nv_bfloat16, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(out), total, inter, block);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}
+
+// out[t, c] = tanh(src[t * stride + c]) for c < width: some columns of a wider activation through
+// tanh, rounded to the output type (the inner activation of a low-rank product).
+template <typename S, typename A>
+__global__ void tanh_columns_kernel(const S* src, long long stride, A* __restrict__ out, int width, size_t total) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / width;
+  out[idx] = from_f32<A>(tanhf(to_f32(src[t * stride + idx % width])));
+}
+
+LRM_API int lrm_tanh_columns(const void* src, int in_dtype, long long stride, void* out, int out_dtype, long long rows,
+                             int width, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (width <= 0 || stride < width) return LRM_BAD_ARGUMENT;
+  const size_t total = static_cast<size_t>(rows) * width;
+  if (in_dtype == LRM_F32 && out_dtype == LRM_F32)
+    LRM_LAUNCH((tanh_columns_kernel<float, float>), blocks_for(total), 256, 0, stream, static_cast<const float*>(src),
+               stride, static_cast<float*>(out), width, total);
+  else if (in_dtype == LRM_F32 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((tanh_columns_kernel<float, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const float*>(src), stride, static_cast<__nv_bfloat16*>(out), width, total);
+  else if (in_dtype == LRM_BF16 && out_dtype == LRM_BF16)
+    LRM_LAUNCH((tanh_columns_kernel<__nv_bfloat16, __nv_bfloat16>), blocks_for(total), 256, 0, stream,
+               static_cast<const __nv_bfloat16*>(src), stride, static_cast<__nv_bfloat16*>(out), width, total);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}

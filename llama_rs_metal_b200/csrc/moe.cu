@@ -61,10 +61,11 @@ __device__ __forceinline__ void score_row(const float* __restrict__ z, const flo
 }
 
 // One thread: the `keep` best of `groups` groups by their largest choice score, then the `top` best
-// allowed outputs; `open` [groups] is scratch. The weights are the chosen s.
+// allowed outputs; `open` [groups] is scratch. The weights are the chosen s, divided by (their sum +
+// mass_eps) with `renormalize`, then times weight_scale.
 __device__ void choose_scored(const float* __restrict__ s, const float* __restrict__ choice, unsigned char* open,
-                              int E, int top, int groups, int keep, int renormalize, int* __restrict__ ids,
-                              float* __restrict__ weights) {
+                              int E, int top, int groups, int keep, int renormalize, float mass_eps,
+                              float weight_scale, int* __restrict__ ids, float* __restrict__ weights) {
   const int size = E / groups;
   if (groups > 1 && keep < groups) {
     for (int g = 0; g < groups; ++g) open[g] = 0;
@@ -103,14 +104,17 @@ __device__ void choose_scored(const float* __restrict__ s, const float* __restri
     mass += s[arg];
   }
   if (renormalize)
-    for (int c = 0; c < top; ++c) weights[c] /= mass;
+    for (int c = 0; c < top; ++c) weights[c] /= mass + mass_eps;
+  if (weight_scale != 1.0f)
+    for (int c = 0; c < top; ++c) weights[c] *= weight_scale;
 }
 
 // Scored routing from logits [T, E]: one warp per token; shared memory per warp: s [E], choice [E],
 // and the groups' flags.
 __global__ void moe_route_scored_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
                                         int* __restrict__ ids, float* __restrict__ weights, int tokens, int E,
-                                        int top, int groups, int keep, int renormalize) {
+                                        int top, int groups, int keep, int renormalize, float mass_eps,
+                                        float weight_scale) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
@@ -124,7 +128,7 @@ __global__ void moe_route_scored_kernel(const float* __restrict__ logits, const 
   __syncwarp();
   if (lane == 0)
     choose_scored(s, choice, reinterpret_cast<unsigned char*>(choice + E), E, top, groups, keep, renormalize,
-                  ids + static_cast<size_t>(t) * top, weights + static_cast<size_t>(t) * top);
+                  mass_eps, weight_scale, ids + static_cast<size_t>(t) * top, weights + static_cast<size_t>(t) * top);
 }
 
 // out[t, :] += (sum of the weights of the identity experts token t chose) * x[t, :]; x is the
@@ -188,7 +192,7 @@ __global__ void moe_router_kernel(const A* __restrict__ x, const float* __restri
                                   const float* __restrict__ bias, int* __restrict__ ids,
                                   float* __restrict__ weights, float* __restrict__ logits, int width, int E,
                                   int top, int scored, const float* __restrict__ correction, int groups, int keep,
-                                  int renormalize) {
+                                  int renormalize, float mass_eps, float weight_scale) {
   extern __shared__ float smem[];
   float* xs = smem;          // [width]
   float* zs = smem + width;  // [E] (scored: also s [E], choice [E] and the groups' flags behind it)
@@ -215,7 +219,7 @@ __global__ void moe_router_kernel(const A* __restrict__ x, const float* __restri
     __syncwarp();
     if (lane == 0)
       choose_scored(zs + E, zs + 2 * E, reinterpret_cast<unsigned char*>(zs + 3 * E), E, top, groups, keep,
-                    renormalize, mine, out);
+                    renormalize, mass_eps, weight_scale, mine, out);
     return;
   }
   if (threadIdx.x != 0) return;
@@ -445,10 +449,12 @@ LRM_API int lrm_moe_route(const float* logits, const float* bias, int* ids, floa
 // x [T, width] float32 or bfloat16 (widened to float32), w float32 [E, width], bias float32 [E] or
 // null -> ids int32 [T, top], weights float32 [T, top]; `logits` (float32 [T, E]) may be null.
 // `scored`: the scored router described at the top (correction float32 [E] or null, `groups` equal
-// groups of which `keep` stay open, `renormalize`); bias is then not used.
+// groups of which `keep` stay open, `renormalize` with mass_eps added to the sum, weight_scale on the weights);
+// bias is then not used.
 LRM_API int lrm_moe_router(const void* x, int x_dtype, const float* w, const float* bias, int* ids,
                            float* weights, float* logits, int tokens, int width, int E, int top, int scored,
-                           const float* correction, int groups, int keep, int renormalize, cudaStream_t stream) {
+                           const float* correction, int groups, int keep, int renormalize, float mass_eps,
+                           float weight_scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (width <= 0 || E <= 0 || top <= 0 || top > E) return LRM_BAD_ARGUMENT;
   if (scored && (groups <= 0 || E % groups || keep <= 0 || keep > groups || top > keep * (E / groups)))
@@ -458,11 +464,11 @@ LRM_API int lrm_moe_router(const void* x, int x_dtype, const float* w, const flo
   const int threads = E >= 8 ? 256 : 128;
   if (x_dtype == LRM_F32)
     LRM_LAUNCH(moe_router_kernel<float>, tokens, threads, bytes, stream, static_cast<const float*>(x), w, bias, ids,
-               weights, logits, width, E, top, scored, correction, groups, keep, renormalize);
+               weights, logits, width, E, top, scored, correction, groups, keep, renormalize, mass_eps, weight_scale);
   else if (x_dtype == LRM_BF16)
     LRM_LAUNCH(moe_router_kernel<__nv_bfloat16>, tokens, threads, bytes, stream,
                static_cast<const __nv_bfloat16*>(x), w, bias, ids, weights, logits, width, E, top, scored, correction,
-               groups, keep, renormalize);
+               groups, keep, renormalize, mass_eps, weight_scale);
   else
     return LRM_BAD_ARGUMENT;
   return 0;
@@ -470,7 +476,8 @@ LRM_API int lrm_moe_router(const void* x, int x_dtype, const float* w, const flo
 
 // The scored router's choice from float32 logits [T, E] -> ids int32 [T, top], weights float32 [T, top].
 LRM_API int lrm_moe_route_scored(const float* logits, const float* correction, int* ids, float* weights, int tokens,
-                                 int E, int top, int groups, int keep, int renormalize, cudaStream_t stream) {
+                                 int E, int top, int groups, int keep, int renormalize, float mass_eps,
+                                 float weight_scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
       top > keep * (E / groups))
@@ -479,7 +486,7 @@ LRM_API int lrm_moe_route_scored(const float* logits, const float* correction, i
   const size_t bytes = sizeof(float) * warps * (2 * static_cast<size_t>(E) + (groups + 3) / 4);
   if (bytes > 48 * 1024) return LRM_UNSUPPORTED;
   LRM_LAUNCH(moe_route_scored_kernel, (tokens + warps - 1) / warps, 32 * warps, bytes, stream, logits, correction, ids,
-             weights, tokens, E, top, groups, keep, renormalize);
+             weights, tokens, E, top, groups, keep, renormalize, mass_eps, weight_scale);
   return 0;
 }
 

@@ -4,10 +4,13 @@
 //   plain decay (retention):   S <- a S + k v^T                      o = S^T q
 //   decay per token:           S <- a_t S + k v^T                    o = S^T q
 //   gated delta rule:          S <- diag(g) S;  u = b (v - S^T k);   S <- S + k u^T;   o = S^T q
+//   generalized delta rule:    S <- diag(g) S + e (c^T S) + k v^T   (both terms read the old S)   o = S^T q
 //
 // with a one decay per head (or, per token, one per head and token: state-space and matrix-memory
 // mixers, whose step size or input gate the caller has multiplied into v), g one decay per head
-// and key channel and token, b one step size per head and token. Everything here is float32: the inputs are prepared in float32 by the kernels
+// and key channel and token, b one step size per head and token; in the generalized rule c is the
+// direction that is read (a unit key) and e what is written back along it (minus a removal rate
+// per key channel times that direction), both per head, key channel and token. Everything here is float32: the inputs are prepared in float32 by the kernels
 // below (rotation, short convolutions, unit norms, decays), the state lives in float32 in the
 // cache's state storage, one matrix per slot and head, and is carried from step to step.
 //
@@ -43,19 +46,24 @@ __device__ __forceinline__ void scan_cp_async(float* dst, const float* src, bool
 // and g rows lie in shared memory as [P][ROWS + 4] (the 4 floats between the parts keep the parts'
 // 16-byte reads on different banks); tokens come in chunks of kChunk, two chunks in flight.
 // MODE 0: one decay per head (head_decay); 1: the gated delta rule (g, beta); 2: one decay per head
-// and token (in `beta`'s place, [T, H]).
+// and token (in `beta`'s place, [T, H]); 3: the generalized delta rule (g, and the two more rows
+// `look` = c and `put` = e per token, [T, H, d]): with t_j = sum_i c_i S_ij over the old state,
+// S_ij <- g_i S_ij + e_i t_j + k_i v_j and o_j = sum_i g_i S_ij q_i + t_j (e . q) + v_j (k . q).
 template <int ROWS, int MODE>
 __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ g, const float* __restrict__ head_decay, const float* __restrict__ beta,
+    const float* __restrict__ look, const float* __restrict__ put,
     float* __restrict__ state, float* __restrict__ out, const int* __restrict__ cu_seqlens,
     const int* __restrict__ slots, int H, int KH, int d, int dv, int P) {
   extern __shared__ __align__(16) float smem[];
   constexpr bool DELTA = MODE == 1;
+  constexpr bool GEN = MODE == 3;
+  constexpr int NR = DELTA ? 3 : GEN ? 5 : 2;          // rows of d floats a token brings
   constexpr int RS = ROWS + 4;
   const int TS = P * RS, COLS = kScanThreads / P;
   const int VS = (COLS + 3) & ~3;                       // v of a token, padded to whole 16 bytes
-  const int TOKEN = (DELTA ? 3 : 2) * TS + VS + 4;      // q | k | (g) | v | beta
+  const int TOKEN = NR * TS + VS + 4;                   // q | k | (g) | (look | put) | v | beta
   const int STAGE = kChunk * TOKEN;
 
   const int tid = threadIdx.x, pidx = tid % P, jl = tid / P;
@@ -87,18 +95,22 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
       float* dst = base + c * TOKEN + (r / ROWS) * RS + r % ROWS;
       scan_cp_async(dst, q + (tok * KH + kh) * d + (in ? r : 0), in, wide);
       scan_cp_async(dst + TS, k + (tok * KH + kh) * d + (in ? r : 0), in, wide);
-      if (DELTA) scan_cp_async(dst + 2 * TS, g + (tok * H + h) * d + (in ? r : 0), in, wide);
+      if (DELTA || GEN) scan_cp_async(dst + 2 * TS, g + (tok * H + h) * d + (in ? r : 0), in, wide);
+      if (GEN) {
+        scan_cp_async(dst + 3 * TS, look + (tok * H + h) * d + (in ? r : 0), in, wide);
+        scan_cp_async(dst + 4 * TS, put + (tok * H + h) * d + (in ? r : 0), in, wide);
+      }
     }
     const int v_per_token = COLS / step;
     for (int idx = tid; idx < cn * v_per_token; idx += kScanThreads) {
       const int c = idx / v_per_token, cl = (idx % v_per_token) * step, col = blockIdx.x * COLS + cl;
       const size_t tok = static_cast<size_t>(start + c0 + c);
       const bool in = col < dv;
-      scan_cp_async(base + c * TOKEN + (DELTA ? 3 : 2) * TS + cl, v + (tok * H + h) * dv + (in ? col : 0), in, wide);
+      scan_cp_async(base + c * TOKEN + NR * TS + cl, v + (tok * H + h) * dv + (in ? col : 0), in, wide);
     }
-    if (MODE != 0)
+    if (MODE == 1 || MODE == 2)
       for (int c = tid; c < cn; c += kScanThreads)
-        scan_cp_async(base + c * TOKEN + (DELTA ? 3 : 2) * TS + VS, beta + static_cast<size_t>(start + c0 + c) * H + h,
+        scan_cp_async(base + c * TOKEN + NR * TS + VS, beta + static_cast<size_t>(start + c0 + c) * H + h,
                       true, false);
     asm volatile("cp.async.commit_group;\n" ::);
   };
@@ -121,14 +133,24 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
       const float* gc = kc + TS;
       const float at = MODE == 2 ? base[c * TOKEN + 2 * TS + VS] : a;
       float kr[ROWS];
-      float r0 = 0.f, r1 = 0.f, s0 = 0.f, s1 = 0.f, kq0 = 0.f, kq1 = 0.f;
+      float er[GEN ? ROWS : 1];
+      float r0 = 0.f, r1 = 0.f, s0 = 0.f, s1 = 0.f, kq0 = 0.f, kq1 = 0.f, eq0 = 0.f, eq1 = 0.f;
 #pragma unroll
       for (int i = 0; i < ROWS; i += 4) {
         const float4 k4 = *reinterpret_cast<const float4*>(kc + i);
         const float4 q4 = *reinterpret_cast<const float4*>(qc + i);
         float4 g4 = make_float4(at, at, at, at);
-        if (DELTA) g4 = *reinterpret_cast<const float4*>(gc + i);
+        if (DELTA || GEN) g4 = *reinterpret_cast<const float4*>(gc + i);
         kr[i] = k4.x, kr[i + 1] = k4.y, kr[i + 2] = k4.z, kr[i + 3] = k4.w;
+        if constexpr (GEN) {  // what the old state holds along `look`, before the decay
+          const float4 c4 = *reinterpret_cast<const float4*>(gc + TS + i);
+          const float4 e4 = *reinterpret_cast<const float4*>(gc + 2 * TS + i);
+          r0 = fmaf(S[i], c4.x, r0), r1 = fmaf(S[i + 1], c4.y, r1);
+          r0 = fmaf(S[i + 2], c4.z, r0), r1 = fmaf(S[i + 3], c4.w, r1);
+          er[i] = e4.x, er[i + 1] = e4.y, er[i + 2] = e4.z, er[i + 3] = e4.w;
+          eq0 = fmaf(e4.x, q4.x, eq0), eq1 = fmaf(e4.y, q4.y, eq1);
+          eq0 = fmaf(e4.z, q4.z, eq0), eq1 = fmaf(e4.w, q4.w, eq1);
+        }
         S[i] *= g4.x, S[i + 1] *= g4.y, S[i + 2] *= g4.z, S[i + 3] *= g4.w;
         if (DELTA) {
           r0 = fmaf(S[i], k4.x, r0), r1 = fmaf(S[i + 1], k4.y, r1);
@@ -139,16 +161,22 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
         kq0 = fmaf(k4.x, q4.x, kq0), kq1 = fmaf(k4.y, q4.y, kq1);
         kq0 = fmaf(k4.z, q4.z, kq0), kq1 = fmaf(k4.w, q4.w, kq1);
       }
-      float r = r0 + r1, s = s0 + s1, kq = kq0 + kq1;
+      float r = r0 + r1, s = s0 + s1, kq = kq0 + kq1, eq = eq0 + eq1;
       for (int o = 1; o < P; o <<= 1) {
-        if (DELTA) r += __shfl_xor_sync(0xffffffffu, r, o);
+        if (DELTA || GEN) r += __shfl_xor_sync(0xffffffffu, r, o);
+        if (GEN) eq += __shfl_xor_sync(0xffffffffu, eq, o);
         s += __shfl_xor_sync(0xffffffffu, s, o);
         kq += __shfl_xor_sync(0xffffffffu, kq, o);
       }
-      const float vj = base[c * TOKEN + (DELTA ? 3 : 2) * TS + jl];
+      const float vj = base[c * TOKEN + NR * TS + jl];
       const float u = DELTA ? base[c * TOKEN + 3 * TS + VS] * (vj - r) : vj;
 #pragma unroll
       for (int i = 0; i < ROWS; ++i) S[i] = fmaf(kr[i], u, S[i]);
+      if constexpr (GEN) {
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) S[i] = fmaf(er[i], r, S[i]);
+        s = fmaf(r, eq, s);
+      }
       if (pidx == 0 && j < dv)
         out[(static_cast<size_t>(start + c0 + c) * H + h) * dv + j] = fmaf(u, kq, s);
     }
@@ -165,11 +193,11 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
 
 template <int ROWS, int MODE>
 int launch_scan(const float* q, const float* k, const float* v, const float* g, const float* head_decay,
-                const float* beta, float* state, float* out, const int* cu_seqlens, const int* slots,
+                const float* beta, const float* look, const float* put, float* state, float* out, const int* cu_seqlens, const int* slots,
                 int seqs, int H, int KH, int d, int dv, int P, cudaStream_t stream) {
-  constexpr bool DELTA = MODE == 1;
+  constexpr int NR = MODE == 1 ? 3 : MODE == 3 ? 5 : 2;
   const int COLS = kScanThreads / P, TS = P * (ROWS + 4), VS = (COLS + 3) & ~3;
-  const size_t bytes = sizeof(float) * 2 * kChunk * (static_cast<size_t>(DELTA ? 3 : 2) * TS + VS + 4);
+  const size_t bytes = sizeof(float) * 2 * kChunk * (static_cast<size_t>(NR) * TS + VS + 4);
   static bool raised = false;  // per instantiation
   if (bytes > 48 * 1024 && !raised) {
     cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<ROWS, MODE>,
@@ -179,7 +207,7 @@ int launch_scan(const float* q, const float* k, const float* v, const float* g, 
   }
   const dim3 grid((dv + COLS - 1) / COLS, H, seqs);
   LRM_LAUNCH((linear_scan_kernel<ROWS, MODE>), grid, kScanThreads, bytes, stream, q, k, v, g, head_decay, beta,
-             state, out, cu_seqlens, slots, H, KH, d, dv, P);
+             look, put, state, out, cu_seqlens, slots, H, KH, d, dv, P);
   return 0;
 }
 
@@ -199,13 +227,13 @@ void scan_shape(int d, int* rows, int* parts) {
 
 template <int MODE>
 int dispatch_scan(const float* q, const float* k, const float* v, const float* g, const float* head_decay,
-                  const float* beta, float* state, float* out, const int* cu_seqlens, const int* slots,
+                  const float* beta, const float* look, const float* put, float* state, float* out, const int* cu_seqlens, const int* slots,
                   int seqs, int H, int KH, int d, int dv, cudaStream_t stream) {
   int R, P;
   scan_shape(d, &R, &P);
 #define LRM_SCAN_CASE(N)                                                                             \
   case N:                                                                                            \
-    return launch_scan<N, MODE>(q, k, v, g, head_decay, beta, state, out, cu_seqlens, slots, seqs, H, \
+    return launch_scan<N, MODE>(q, k, v, g, head_decay, beta, look, put, state, out, cu_seqlens, slots, seqs, H, \
                                  KH, d, dv, P, stream)
   switch (R) {
     LRM_SCAN_CASE(4);
@@ -423,14 +451,27 @@ LRM_API int lrm_linear_state_scan(const float* q, const float* k, const float* v
   if (d > 2048) return LRM_UNSUPPORTED;
   if (g != nullptr) {
     if (beta == nullptr) return LRM_BAD_ARGUMENT;
-    return dispatch_scan<1>(q, k, v, g, nullptr, beta, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
+    return dispatch_scan<1>(q, k, v, g, nullptr, beta, nullptr, nullptr, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
   }
   if (head_decay == nullptr) {  // one decay per head and token, where beta would be
     if (beta == nullptr) return LRM_BAD_ARGUMENT;
-    return dispatch_scan<2>(q, k, v, nullptr, nullptr, beta, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
+    return dispatch_scan<2>(q, k, v, nullptr, nullptr, beta, nullptr, nullptr, state, out, cu_seqlens, slots, seqs, H, KH, d, dv, stream);
   }
-  return dispatch_scan<0>(q, k, v, nullptr, head_decay, nullptr, state, out, cu_seqlens, slots, seqs, H, KH, d,
+  return dispatch_scan<0>(q, k, v, nullptr, head_decay, nullptr, nullptr, nullptr, state, out, cu_seqlens, slots, seqs, H, KH, d,
                           dv, stream);
+}
+
+// The generalized delta rule: q, k, v, g as above (one key head per head), look and put float32
+// [T, H, d]: S <- diag(g) S + put (look^T S) + k v^T with both terms reading the old S; o = S^T q.
+LRM_API int lrm_general_delta_scan(const float* q, const float* k, const float* v, const float* g, const float* look,
+                                   const float* put, float* state, float* out, const int* cu_seqlens,
+                                   const int* slots, int seqs, int H, int d, int dv, cudaStream_t stream) {
+  if (seqs <= 0) return 0;
+  if (H <= 0 || d <= 0 || dv <= 0 || seqs > 65535 || H > 65535) return LRM_BAD_ARGUMENT;
+  if (g == nullptr || look == nullptr || put == nullptr) return LRM_BAD_ARGUMENT;
+  if (d > 2048) return LRM_UNSUPPORTED;
+  return dispatch_scan<3>(q, k, v, g, nullptr, nullptr, look, put, state, out, cu_seqlens, slots, seqs, H, H, d, dv,
+                          stream);
 }
 
 // `gate` (type gate_dtype, may be null) is read at gate[t * gate_stride + h * dv + j]; o at

@@ -1,0 +1,95 @@
+// What a block does to the stream around its sublayers beyond norms: the mix of a sublayer's input
+// with the previous token's, and the addition of a sublayer's output under a factor per channel.
+#include "common.cuh"
+
+namespace {
+
+// out[t, c] = h[t, c] + (h[t - 1, c] - h[t, c]) * mix[c], with the previous token's row as it was
+// before this replacement; for a sequence's first token of the step it comes from `last`
+// [slots, width] (float32; zeros at the start of a sequence), and a sequence of padding (slot < 0)
+// has zeros there. One CTA per token. The caller rewrites `last` afterwards (conv_tail_update with
+// two taps keeps exactly this row).
+template <typename A>
+__global__ void token_shift_kernel(const A* h, const float* __restrict__ mix, const float* last, A* __restrict__ out,
+                                   const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token,
+                                   const int* __restrict__ slots, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int b = seq_of_token[t], local = t - cu_seqlens[b], slot = slots[b];
+  const A* row = h + static_cast<size_t>(t) * width;
+  const A* before = local > 0 ? row - width : nullptr;
+  const float* kept = (local == 0 && slot >= 0) ? last + static_cast<size_t>(slot) * width : nullptr;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float x = to_f32(row[c]);
+    const float p = before != nullptr ? to_f32(before[c]) : kept != nullptr ? kept[c] : 0.f;
+    out[static_cast<size_t>(t) * width + c] = from_f32<A>(fmaf(p - x, mix[c], x));
+  }
+}
+
+// x[t, c] += factor[c] * y[t, c]: a sublayer's float32 output enters the float32 stream under a
+// factor per channel.
+__global__ void scaled_add_kernel(float* x, const float* y, const float* __restrict__ factor, int width, size_t n) {
+  pdl_trigger();
+  pdl_wait();
+  const size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
+  if (idx < n) x[idx] = fmaf(factor[idx % width], y[idx], x[idx]);
+}
+
+// y[t, :] *= sigmoid(x[t, :] . w): one gate per token from its input row (float32 sum), on a
+// float32 output row. One CTA per token.
+template <typename A>
+__global__ void row_gate_kernel(float* y, const A* x, const float* __restrict__ w, int in_width, int out_width) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  float acc = 0.f;
+  for (int c = threadIdx.x; c < in_width; c += blockDim.x)
+    acc = fmaf(to_f32(x[static_cast<size_t>(t) * in_width + c]), w[c], acc);
+  const float z = block_sum(acc, scratch);
+  const float gate = 1.0f / (1.0f + expf(-z));
+  for (int c = threadIdx.x; c < out_width; c += blockDim.x) y[static_cast<size_t>(t) * out_width + c] *= gate;
+}
+
+}  // namespace
+
+LRM_API int lrm_token_shift(const void* h, int dtype, const float* mix, const float* last, void* out,
+                            const int* cu_seqlens, const int* seq_of_token, const int* slots, int tokens, int width,
+                            cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (width <= 0 || mix == nullptr || last == nullptr) return LRM_BAD_ARGUMENT;
+  const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+  if (dtype == LRM_F32)
+    LRM_LAUNCH(token_shift_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(h), mix, last,
+               static_cast<float*>(out), cu_seqlens, seq_of_token, slots, width);
+  else if (dtype == LRM_BF16)
+    LRM_LAUNCH(token_shift_kernel<__nv_bfloat16>, tokens, threads, 0, stream, static_cast<const __nv_bfloat16*>(h),
+               mix, last, static_cast<__nv_bfloat16*>(out), cu_seqlens, seq_of_token, slots, width);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}
+
+LRM_API int lrm_scaled_add(float* x, const float* y, const float* factor, long long rows, int width,
+                           cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (x == nullptr || y == nullptr || factor == nullptr || width <= 0) return LRM_BAD_ARGUMENT;
+  const size_t n = static_cast<size_t>(rows) * width;
+  LRM_LAUNCH(scaled_add_kernel, static_cast<unsigned>((n + 255) / 256), 256, 0, stream, x, y, factor, width, n);
+  return 0;
+}
+
+LRM_API int lrm_row_gate(float* y, const void* x, int x_dtype, const float* w, int tokens, int in_width, int out_width,
+                         cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (y == nullptr || w == nullptr || in_width <= 0 || out_width <= 0) return LRM_BAD_ARGUMENT;
+  if (x_dtype == LRM_F32)
+    LRM_LAUNCH(row_gate_kernel<float>, tokens, 256, 0, stream, y, static_cast<const float*>(x), w, in_width, out_width);
+  else if (x_dtype == LRM_BF16)
+    LRM_LAUNCH(row_gate_kernel<__nv_bfloat16>, tokens, 256, 0, stream, y, static_cast<const __nv_bfloat16*>(x), w,
+               in_width, out_width);
+  else
+    return LRM_BAD_ARGUMENT;
+  return 0;
+}

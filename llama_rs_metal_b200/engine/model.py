@@ -32,6 +32,7 @@ class DecoderModel:
         self.plan, self.runtime = plan, runtime
         self.blocks: List[Block] = []
         self._names: List[Dict[str, Dict[str, str]]] = []
+        self._block_names: List[Dict[str, str]] = []
         for layer in plan.layers:
             if layer.block not in BLOCKS:
                 raise InvalidError(f"block kind {layer.block!r} is not registered")
@@ -50,6 +51,8 @@ class DecoderModel:
                 raise InvalidError(f"a {layer.block!r} layer has no role {', '.join(unknown)}")
             self.blocks.append(block_class(**parts, **layer.options))
             self._names.append({role: _full_names(layer.parts[role], part) for role, part in parts.items()})
+            # tensors the arrangement itself owns (a factor per channel on what a sublayer adds, ...)
+            self._block_names.append({own: layer.names.get(own, own) for own in self.blocks[-1].tensors()})
         self.final_norm = build_part(NORMS, plan.final_norm, "norm")
         self._final_names = _full_names(plan.final_norm, self.final_norm)
         self.embedding: Optional[torch.Tensor] = None
@@ -101,11 +104,14 @@ class DecoderModel:
             specs[plan.head_name] = TensorSpec((plan.vocab_size, plan.hidden_size))
         if plan.stream_offsets is not None:
             specs[plan.stream_offsets[0]] = TensorSpec((plan.stream_offsets[1], plan.hidden_size))
-        for block, names in zip(self.blocks, self._names):
+        for block, names, own_names in zip(self.blocks, self._names, self._block_names):
             for role, mapping in names.items():
                 part_specs = getattr(block, role).tensors()
                 for own, full in mapping.items():
                     specs[full] = part_specs[own]
+            block_specs = block.tensors()
+            for own, full in own_names.items():
+                specs[full] = block_specs[own]
         for own, full in self._final_names.items():
             specs[full] = self.final_norm.tensors()[own]
         return specs
@@ -118,9 +124,10 @@ class DecoderModel:
         self.head = LinearWeight(head)
         if self.plan.stream_offsets is not None:  # added to the float32 stream: kept in float32
             self.stream_offsets = tensors[self.plan.stream_offsets[0]].to(torch.float32).contiguous()
-        for block, names in zip(self.blocks, self._names):
+        for block, names, own_names in zip(self.blocks, self._names, self._block_names):
             for role, mapping in names.items():
                 getattr(block, role).bind({own: tensors[full] for own, full in mapping.items()}, rt)
+            block.bind({own: tensors[full] for own, full in own_names.items()}, rt)
         self.final_norm.bind({own: tensors[full] for own, full in self._final_names.items()}, rt)
 
     # -- forward ---------------------------------------------------------------------
@@ -164,6 +171,7 @@ class DecoderModel:
         hidden = ops.embed_rows(self.embedding, ctx.token_ids, plan.embedding_scale)
         wanted = ctx.wanted_rows.numel() > 0
         schedule = plan.schedule
+        embedded = hidden.clone() if any(entry.add_embedding for entry in schedule) else None
         for i, entry in enumerate(schedule):
             ctx.entry = entry
             view = cache.view(entry.cache) if cache is not None else None
@@ -173,10 +181,13 @@ class DecoderModel:
                 ctx.next_folds_pending = following.folds_pending_on_entry
                 # a block may hand the next one its stream already passed through that block's
                 # first norm (nothing may be added to the stream in between)
-                ctx.next_entry_norm = following.entry_norm if schedule[i + 1].add_offset is None else None
+                ctx.next_entry_norm = following.entry_norm \
+                    if schedule[i + 1].add_offset is None and not schedule[i + 1].add_embedding else None
             else:
                 ctx.next_folds_pending = wanted and self.final_norm.folds_pending
                 ctx.next_entry_norm = None
+            if entry.add_embedding:
+                hidden = ops.add_(ctx.settle(hidden), embedded)
             if entry.add_offset is not None:
                 hidden = ops.add_row_(hidden, self.stream_offsets[entry.add_offset])
             hidden = self.blocks[entry.layer].forward(hidden, ctx, view)

@@ -62,6 +62,31 @@ class Extras:
 NO_EXTRAS = Extras()
 
 
+@dataclass(frozen=True)
+class Shaping:
+    """What some attention layers do to their queries and keys between the projection and the
+    attention itself (csrc/shaped_qkv.cu applies it in this order, each step only if given).
+
+    taps: float32 [projection row, n], a causal convolution over time on every projected channel,
+        with `tails`, the StateView of the sequences' last n - 1 unbiased projections.
+    row_norm: (q weight, k weight), an RMS norm over all query columns and one over all key columns
+        (eps `row_eps`).
+    inv_freq, rotary, adjacent_pairs: a rotation of each head's first `rotary` dimensions, angle =
+        position * inv_freq[i] (float64 [rotary / 2]); dimension i pairs with i + rotary / 2, or 2i
+        with 2i + 1.
+    head_norm_eps: each query and key head is divided by its root mean square afterwards.
+    """
+
+    taps: Optional[torch.Tensor] = None
+    tails: Optional[object] = None
+    row_norm: Optional[tuple] = None
+    row_eps: float = 0.0
+    inv_freq: Optional[torch.Tensor] = None
+    rotary: int = 0
+    adjacent_pairs: bool = False
+    head_norm_eps: Optional[float] = None
+
+
 def _value_stride(kv) -> int:
     """Elements between two value rows of a cache view: values that live inside the key rows are
     read from the keys' storage with the keys' width."""
@@ -118,7 +143,7 @@ def prefill(q, k, v, out, cu_seqlens, seq_of_token, max_seq_len: int, scale: flo
         return
     dv = v.shape[2]
     aligned = all(t.data_ptr() % 16 == 0 for t in (q, k, v, out))
-    if (not force_rowwise and not force_warp_level and q.dtype == torch.bfloat16 and aligned
+    if (not force_rowwise and not force_warp_level and q.dtype == torch.bfloat16 and aligned and window >= 0
             and _plain(q, dv, slopes, out_scale) and lib.lrm_attention_prefill_umma_supports(d)):
         from . import gemm_dispatch
         gemm_dispatch.mark_status_dirty()
@@ -169,7 +194,7 @@ CTAS_PER_SM = 4  # decode attention CTAs wanted per SM (each keeps one 64-key K/
 def decode_splits(seqs: int, kv_heads: int, group: int, max_kv_len: int, window: int) -> int:
     """Splits of the key range so that about CTAS_PER_SM CTAs per SM stream the cache."""
     ctas = seqs * kv_heads * -(-group // 16)
-    keys = min(max_kv_len, window + 63) if window > 0 else max_kv_len
+    keys = min(max_kv_len, abs(window) + 63) if window else max_kv_len  # a chunk (window < 0) shows no more either
     pages = max(1, -(-keys // 64))
     return max(1, min(pages, -(-CTAS_PER_SM * SM_COUNT // ctas)))
 
@@ -341,7 +366,8 @@ def decode_fused(qkv, positions, inv_freq, rotary: int, kv, dest_rows, out, slot
 # --------------------------------------------------------------------------- one call for a mixer
 def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx, cache, writes_cache: bool,
            cache_entry: int, scale: float, window, projection=None, value_dim=None, bias=None, slopes=None,
-           out_scale: float = 1.0, extras=None, values_are_keys: bool = False):
+           out_scale: float = 1.0, extras=None, values_are_keys: bool = False, shaping: Optional[Shaping] = None,
+           chunk: Optional[int] = None):
     """A layer's attention for one step: position rotation, cache write and attention, with the
     kernels chosen here for the step's phase, dtype and geometry. -> mixed heads [T, q_heads * d].
 
@@ -359,6 +385,10 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
         the projection is q|k only and a key row is also its value row. With any of these the split
         kernel without rotation (csrc/qkv_store.cu) takes the place of the rotation kernel, and
         attention runs on the kernels that know them.
+    shaping: a Shaping; the split kernel is then csrc/shaped_qkv.cu, which also rotates (`rotary`
+        stays None) and takes the projection in float32. chunk: positions form chunks of this many,
+        counted from position 0, and a query sees only the keys of its own chunk (`window` is then
+        what the cache keeps, and the kernels are told the chunk as a negative window).
     """
     from . import ops
     inv_freq, width = rotary if rotary is not None else (None, 0)
@@ -366,7 +396,10 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
     dv = head_dim if value_dim is None else value_dim
     if values_are_keys:
         dv = 0  # the projection has no value columns
-    if bias is not None or dv != head_dim or slopes is not None or out_scale != 1.0 or extras is not None:
+    if chunk:
+        window = -int(chunk)
+    if (bias is not None or dv != head_dim or slopes is not None or out_scale != 1.0 or extras is not None
+            or shaping is not None or chunk):
         if inv_freq is not None:
             from ..errors import UnsupportedError
             raise UnsupportedError("attention with a bias, a distance penalty or values of another width "
@@ -374,10 +407,20 @@ def attend(projected, *, q_heads: int, kv_heads: int, head_dim: int, rotary, ctx
         if projection is not None:
             projected = ops.linear(*projection)
         prefill_phase = phase == "prefill"
-        q, k, v = ops.qkv_bias_store(projected, bias, q_heads, kv_heads if writes_cache else 0, head_dim, dv,
-                                     kv=cache if writes_cache else None,
-                                     dest_rows=ctx.dest_rows[cache.group] if writes_cache and cache is not None else None,
-                                     keep_packed=prefill_phase and writes_cache)
+        stored = dict(kv=cache if writes_cache else None,
+                      dest_rows=ctx.dest_rows[cache.group] if writes_cache and cache is not None else None,
+                      keep_packed=prefill_phase and writes_cache)
+        if shaping is not None:
+            s = shaping
+            q, k, v = ops.shaped_qkv_store(
+                projected, q_heads, kv_heads if writes_cache else 0, head_dim, dv, ctx.positions, ctx.runtime.dtype,
+                bias=bias, taps=s.taps, tails=s.tails.state if s.tails is not None else None,
+                cu_seqlens=ctx.cu_seqlens, seq_of_token=ctx.seq_of_token, slots=ctx.slots, row_norm=s.row_norm,
+                row_eps=s.row_eps, inv_freq=s.inv_freq, rotary=s.rotary, adjacent_pairs=s.adjacent_pairs,
+                head_norm_eps=s.head_norm_eps, **stored)
+        else:
+            q, k, v = ops.qkv_bias_store(projected, bias, q_heads, kv_heads if writes_cache else 0, head_dim, dv,
+                                         **stored)
         if prefill_phase:
             if writes_cache:
                 ctx.fresh_kv[cache_entry] = (k, k if values_are_keys else v)

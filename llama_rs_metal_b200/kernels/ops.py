@@ -319,6 +319,75 @@ def relu_squared(x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> to
     return out
 
 
+def gelu_tanh_mul(gate_up: torch.Tensor, block: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """gelu(gate) * up with the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), from
+    [T, 2I] whose columns alternate in blocks of `block` gate / up (float32, or the output's type)."""
+    _check(gate_up, "gate_up", dims=2)
+    inter = gate_up.shape[1] // 2
+    if gate_up.shape[1] % 2 or inter % block:
+        raise InvalidError("gelu_tanh_mul: width must be 2*I with I a multiple of the block")
+    out_dtype = out_dtype or gate_up.dtype
+    out = _activation(gate_up.shape[0], inter, out_dtype, gate_up.device)
+    _done(_lib().lrm_gelu_tanh_mul(_ptr(gate_up), _code(gate_up.dtype), _ptr(out), _code(out_dtype),
+                                   ctypes.c_longlong(gate_up.shape[0]), inter, block, _stream()), "gelu_tanh_mul")
+    return out
+
+
+def tanh_columns(src: torch.Tensor, column: int, width: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """tanh of the columns column .. column + width of src [T, W] -> [T, width] in `out_dtype`."""
+    _check(src, "src", dims=2)
+    if width <= 0 or column < 0 or column + width > src.shape[1]:
+        raise InvalidError("tanh_columns: columns outside the activation")
+    out = _activation(src.shape[0], width, out_dtype, src.device)
+    _done(_lib().lrm_tanh_columns(_column_ptr(src, column), _code(src.dtype), ctypes.c_longlong(src.shape[1]), _ptr(out),
+                                  _code(out_dtype), ctypes.c_longlong(src.shape[0]), width, _stream()), "tanh_columns")
+    return out
+
+
+def token_shift(h: torch.Tensor, mix: torch.Tensor, last: torch.Tensor, cu_seqlens: torch.Tensor,
+                seq_of_token: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+    """h[t] + (h[t-1] - h[t]) * mix per channel, h [T, W] packed sequences; the row before a sequence's
+    first token of the step is last[slot] (float32 [slots, 1, W]: the sequence's previous h, zeros at
+    its start). `last` is then rewritten with every sequence's newest row of h."""
+    _check(h, "h", dims=2)
+    _check(mix, "mix", torch.float32, 1)
+    _check(last, "last", torch.float32, 3)
+    T, W = h.shape
+    if mix.numel() != W or tuple(last.shape[1:]) != (1, W):
+        raise InvalidError("token_shift: shapes do not agree")
+    for name, t in (("cu_seqlens", cu_seqlens), ("seq_of_token", seq_of_token), ("slots", slots)):
+        _check(t, name, torch.int32, 1)
+    out = _activation(T, W, h.dtype, h.device)
+    _done(_lib().lrm_token_shift(_ptr(h), _code(h.dtype), _ptr(mix), _ptr(last), _ptr(out), _ptr(cu_seqlens),
+                                 _ptr(seq_of_token), _ptr(slots), T, W, _stream()), "token_shift")
+    conv_tail_update_(h, 0, W, 2, last, cu_seqlens, slots)
+    return out
+
+
+def scaled_add_(x: torch.Tensor, y: torch.Tensor, factor: torch.Tensor) -> torch.Tensor:
+    """x[t, :] += factor * y[t, :] with one factor per column; all float32."""
+    _check(x, "x", torch.float32, 2)
+    _check(y, "y", torch.float32, 2)
+    _check(factor, "factor", torch.float32, 1)
+    if x.shape != y.shape or factor.numel() != x.shape[1]:
+        raise InvalidError("scaled_add_: shapes do not agree")
+    _done(_lib().lrm_scaled_add(_ptr(x), _ptr(y), _ptr(factor), ctypes.c_longlong(x.shape[0]), x.shape[1], _stream()),
+          "scaled_add_")
+    return x
+
+
+def row_gate_(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """y[t, :] *= sigmoid(x[t, :] . weight): y float32 [T, N], x [T, W], weight float32 [W]."""
+    _check(y, "y", torch.float32, 2)
+    _check(x, "x", dims=2)
+    _check(weight, "weight", torch.float32, 1)
+    if x.shape[0] != y.shape[0] or weight.numel() != x.shape[1]:
+        raise InvalidError("row_gate_: shapes do not agree")
+    _done(_lib().lrm_row_gate(_ptr(y), _ptr(x), _code(x.dtype), _ptr(weight), y.shape[0], x.shape[1], y.shape[1],
+                              _stream()), "row_gate_")
+    return y
+
+
 def add_(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
     """x += delta, x float32 (the residual sum is always 32-bit)."""
     _check(x, "x", torch.float32)
@@ -456,6 +525,90 @@ def qkv_bias_store(qkv: torch.Tensor, bias: Optional[torch.Tensor], q_heads: int
     return q, k, v
 
 
+def shaped_qkv_store(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, value_dim: int,
+                     positions: torch.Tensor, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None,
+                     taps: Optional[torch.Tensor] = None, tails: Optional[torch.Tensor] = None,
+                     cu_seqlens: Optional[torch.Tensor] = None, seq_of_token: Optional[torch.Tensor] = None,
+                     slots: Optional[torch.Tensor] = None, row_norm=None, row_eps: float = 0.0,
+                     inv_freq: Optional[torch.Tensor] = None, rotary: int = 0, adjacent_pairs: bool = False,
+                     head_norm_eps: Optional[float] = None, kv=None, dest_rows: Optional[torch.Tensor] = None,
+                     keep_packed: bool = True):
+    """Split a fused [T, Hq*d + Hk*d + Hk*dv] projection (float32, or `out_dtype`) whose queries and
+    keys are shaped on the way, each step only if asked for and in this order: `bias` (float32
+    [row]); a causal convolution per channel (`taps` float32 [row, n] with the sequences' `tails`
+    float32 [slots, n - 1, row] of unbiased projections, rewritten afterwards); an RMS norm over all
+    query columns and one over all key columns (`row_norm` = (q weight, k weight), `row_eps`); the
+    rotation of each head's first `rotary` dimensions by `inv_freq` (float64 [rotary/2]; split halves,
+    or neighbours with `adjacent_pairs`); each head divided by its root mean square
+    (`head_norm_eps`). Returns (q [T,Hq,d], k, v) like qkv_bias_store, and writes the cache view."""
+    _check(qkv, "qkv", dims=2)
+    T = qkv.shape[0]
+    width = q_heads * head_dim + kv_heads * (head_dim + value_dim)
+    if qkv.shape[1] != width:
+        raise InvalidError("shaped_qkv_store: qkv width does not match the head geometry")
+    _check(positions, "positions", torch.int32, 1)
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.numel() != width:
+            raise InvalidError("shaped_qkv_store: one bias per projected column")
+    n = 0
+    if taps is not None:
+        _check(taps, "taps", torch.float32, 2)
+        n = taps.shape[1]
+        if taps.shape[0] != width:
+            raise InvalidError("shaped_qkv_store: one row of taps per projected column")
+        if n > 1:
+            _check(tails, "tails", torch.float32, 3)
+            if tuple(tails.shape[1:]) != (n - 1, width):
+                raise InvalidError("shaped_qkv_store: tails must be [slots, taps - 1, row]")
+            for name, t in (("cu_seqlens", cu_seqlens), ("seq_of_token", seq_of_token), ("slots", slots)):
+                _check(t, name, torch.int32, 1)
+    q_norm = k_norm = None
+    if row_norm is not None:
+        q_norm, k_norm = row_norm
+        _check(q_norm, "q norm", torch.float32, 1)
+        if q_norm.numel() != q_heads * head_dim:
+            raise InvalidError("shaped_qkv_store: the query norm's weight covers all query columns")
+        if kv_heads:
+            _check(k_norm, "k norm", torch.float32, 1)
+            if k_norm.numel() != kv_heads * head_dim:
+                raise InvalidError("shaped_qkv_store: the key norm's weight covers all key columns")
+        else:
+            k_norm = None
+    if rotary:
+        _check(inv_freq, "inv_freq", torch.float64, 1)
+        if inv_freq.numel() != rotary // 2 or rotary % 2 or rotary > head_dim:
+            raise InvalidError("shaped_qkv_store: one frequency per rotated pair")
+    dev = qkv.device
+    q = torch.empty((T, q_heads, head_dim), dtype=out_dtype, device=dev)
+    k = torch.empty((T, kv_heads, head_dim), dtype=out_dtype, device=dev) if keep_packed and kv_heads else None
+    v = torch.empty((T, kv_heads, value_dim), dtype=out_dtype, device=dev) if keep_packed and kv_heads and value_dim else None
+    k_pages = v_pages = None
+    page_size = 1
+    if kv is not None and kv_heads > 0:
+        k_pages, v_pages, page_size = kv.k, kv.v if value_dim else None, kv.page_size
+        _check(k_pages, "k pages", out_dtype, 4)
+        if value_dim:
+            _check(v_pages, "v pages", out_dtype, 4)
+        _check(dest_rows, "dest_rows", torch.int32, 1)
+        if dest_rows.numel() != T:
+            raise InvalidError("shaped_qkv_store: one destination row per token")
+        if (tuple(k_pages.shape[1:]) != (kv_heads, page_size, head_dim)
+                or (value_dim and tuple(v_pages.shape[1:]) != (kv_heads, page_size, value_dim))):
+            raise InvalidError("shaped_qkv_store: cache pages do not match the head geometry")
+    _done(_lib().lrm_shaped_qkv_store(
+        _ptr(qkv), _code(qkv.dtype), _ptr(bias), _ptr(taps), n, _ptr(tails if n > 1 else None),
+        _ptr(cu_seqlens if n > 1 else None), _ptr(seq_of_token if n > 1 else None), _ptr(slots if n > 1 else None),
+        _ptr(positions), _ptr(q_norm), _ptr(k_norm), ctypes.c_float(row_eps), _ptr(inv_freq if rotary else None),
+        rotary, int(bool(adjacent_pairs)), int(head_norm_eps is not None),
+        ctypes.c_float(head_norm_eps if head_norm_eps is not None else 0.0), _ptr(q), _ptr(k), _ptr(v),
+        _ptr(k_pages), _ptr(v_pages), _ptr(dest_rows if k_pages is not None else None), _code(out_dtype), T, q_heads,
+        kv_heads, head_dim, value_dim, page_size, _stream()), "shaped_qkv_store")
+    if n > 1:
+        conv_tail_update_(qkv, 0, width, n, tails, cu_seqlens, slots)
+    return q, k, v
+
+
 # --------------------------------------------------------------------------- fixed-size state mixers
 def _f32(shape, device) -> torch.Tensor:
     return torch.empty(shape, dtype=torch.float32, device=device)
@@ -564,6 +717,57 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: 
     _done(_lib().lrm_linear_state_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(head_decay), _ptr(beta), _ptr(state),
                                        _ptr(out), _ptr(cu_seqlens), _ptr(slots), slots.numel(), H, KH, d, dv,
                                        _stream()), "linear_state_scan")
+    return out
+
+
+def general_delta_prepare(proj: torch.Tensor, r_off: int, k_off: int, v_off: int, a_off: int, z: torch.Tensor,
+                          z_bias: torch.Tensor, a_bias: torch.Tensor, decay_scale: float, unit_eps: float,
+                          heads: int, head_dim: int, value_dim: int):
+    """Inputs of the generalized delta rule from a fused projection [T, W] (r, k, a at their columns,
+    each [heads*d]; v [heads*dv]) and the decay's float32 pre-activation z [T, heads*d]:
+    g = exp(-decay_scale sigmoid(z + z_bias)), look = k / sqrt(sum k^2 + unit_eps) per head,
+    put = -sigmoid(a + a_bias) look. -> r, k, v, g, look, put, all float32 [T, heads, d or dv]."""
+    _check(proj, "proj", dims=2)
+    _check(z, "z", torch.float32, 2)
+    T, W = proj.shape
+    n = heads * head_dim
+    for name, t in (("z_bias", z_bias), ("a_bias", a_bias)):
+        _check(t, name, torch.float32, 1)
+        if t.numel() != n:
+            raise InvalidError(f"general_delta_prepare: {name} has one entry per head and key channel")
+    if tuple(z.shape) != (T, n) or max(r_off, k_off, a_off) + n > W or v_off + heads * value_dim > W:
+        raise InvalidError("general_delta_prepare: columns outside the projection")
+    dev = proj.device
+    r, k, g, look, put = (_f32((T, heads, head_dim), dev) for _ in range(5))
+    v = _f32((T, heads, value_dim), dev)
+    _done(_lib().lrm_general_delta_prepare(_ptr(proj), _code(proj.dtype), ctypes.c_longlong(W), r_off, k_off, v_off,
+                                           a_off, _ptr(z), _ptr(z_bias), _ptr(a_bias), ctypes.c_float(decay_scale),
+                                           ctypes.c_float(unit_eps), _ptr(r), _ptr(k), _ptr(v), _ptr(g), _ptr(look),
+                                           _ptr(put), T, heads, head_dim, value_dim, _stream()),
+          "general_delta_prepare")
+    return r, k, v, g, look, put
+
+
+def general_delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, look: torch.Tensor,
+                       put: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor,
+                       slots: torch.Tensor) -> torch.Tensor:
+    """The generalized delta rule on the per-sequence, per-head matrix state (float32 [slots, H, d, dv],
+    updated in place): S <- diag(g) S + put (look^T S) + k v^T, both terms reading the old S; o = S^T q
+    after the update. q, k, g, look, put float32 [T,H,d], v float32 [T,H,dv]. -> o float32 [T,H,dv]."""
+    for name, t, dims in (("q", q, 3), ("k", k, 3), ("v", v, 3), ("g", g, 3), ("look", look, 3), ("put", put, 3),
+                          ("state", state, 4)):
+        _check(t, name, torch.float32, dims)
+    _check(cu_seqlens, "cu_seqlens", torch.int32, 1)
+    _check(slots, "slots", torch.int32, 1)
+    T, H, d = q.shape
+    dv = v.shape[2]
+    if any(t.shape != q.shape for t in (k, g, look, put)) or tuple(v.shape[:2]) != (T, H) \
+            or tuple(state.shape[1:]) != (H, d, dv):
+        raise InvalidError("general_delta_scan: shapes do not agree")
+    out = _f32((T, H, dv), q.device)
+    _done(_lib().lrm_general_delta_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(g), _ptr(look), _ptr(put), _ptr(state),
+                                        _ptr(out), _ptr(cu_seqlens), _ptr(slots), slots.numel(), H, d, dv, _stream()),
+          "general_delta_scan")
     return out
 
 
@@ -922,15 +1126,18 @@ class Scoring:
     """A router that scores with the softmax over all its outputs: the choice is made on the scores
     plus `correction` (float32 [E] or None), among the outputs of the `keep` best of `groups` equal
     groups of neighbours (a group counts by its largest corrected score); the weights are the
-    chosen scores, divided by their sum with `renormalize`."""
+    chosen scores, divided by (their sum + `mass_eps`) with `renormalize`, then times `weight_scale`."""
 
     correction: Optional[torch.Tensor] = None
     groups: int = 1
     keep: int = 1
     renormalize: bool = False
+    mass_eps: float = 0.0
+    weight_scale: float = 1.0
 
     def arguments(self):
-        return _ptr(self.correction), self.groups, self.keep, int(self.renormalize)
+        return (_ptr(self.correction), self.groups, self.keep, int(self.renormalize), ctypes.c_float(self.mass_eps),
+                ctypes.c_float(self.weight_scale))
 
 
 def moe_route_scored(logits: torch.Tensor, top: int, scoring: Scoring):
@@ -942,7 +1149,7 @@ def moe_route_scored(logits: torch.Tensor, top: int, scoring: Scoring):
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     weights = _f32((T, top), logits.device)
     _done(_lib().lrm_moe_route_scored(_ptr(logits), _ptr(scoring.correction), _ptr(ids), _ptr(weights), T, E, top,
-                                      scoring.groups, scoring.keep, int(scoring.renormalize), _stream()),
+                                      *scoring.arguments()[1:], _stream()),
           "moe_route_scored")
     return ids, weights
 
@@ -992,7 +1199,7 @@ def moe_router(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tenso
         return None
     ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
     weights = _f32((T, top), x.device)
-    extra = (1, *scoring.arguments()) if scoring is not None else (0, None, 1, 1, 0)
+    extra = (1, *scoring.arguments()) if scoring is not None else (0, None, 1, 1, 0, ctypes.c_float(0.0), ctypes.c_float(1.0))
     _done(_lib().lrm_moe_router(_ptr(x), _code(x.dtype), _ptr(weight), _ptr(bias), _ptr(ids), _ptr(weights), None,
                                 T, width, E, top, *extra, _stream()), "moe_router")
     return ids, weights

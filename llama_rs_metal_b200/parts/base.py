@@ -40,11 +40,12 @@ class LayerSpec:
     can be given by name; any other set goes in `parts`.
     """
 
-    __slots__ = ("block", "parts", "options")
+    __slots__ = ("block", "parts", "options", "names")
 
     def __init__(self, block: str, mixer: Optional[PartSpec] = None, feed_forward: Optional[PartSpec] = None,
                  mixer_norm: Optional[PartSpec] = None, feed_forward_norm: Optional[PartSpec] = None,
-                 parts: Optional[Mapping[str, PartSpec]] = None, options: Optional[Mapping[str, Any]] = None):
+                 parts: Optional[Mapping[str, PartSpec]] = None, options: Optional[Mapping[str, Any]] = None,
+                 names: Optional[Mapping[str, str]] = None):
         named = {"mixer": mixer, "feed_forward": feed_forward, "mixer_norm": mixer_norm,
                  "feed_forward_norm": feed_forward_norm}
         merged = {role: spec for role, spec in named.items() if spec is not None}
@@ -54,6 +55,8 @@ class LayerSpec:
         # constants of the arrangement itself (a factor on what a sublayer adds), passed to the
         # block's constructor by keyword beside its parts
         object.__setattr__(self, "options", dict(options or {}))
+        # checkpoint names of the tensors the block itself owns (Block.tensors(): own name -> full name)
+        object.__setattr__(self, "names", dict(names or {}))
 
     def __setattr__(self, name, value):
         raise AttributeError("LayerSpec is immutable; use with_parts()")
@@ -67,7 +70,7 @@ class LayerSpec:
 
     def with_parts(self, **changes: PartSpec) -> "LayerSpec":
         """A copy with some roles' parts replaced or added."""
-        return LayerSpec(self.block, parts={**self.parts, **changes}, options=self.options)
+        return LayerSpec(self.block, parts={**self.parts, **changes}, options=self.options, names=self.names)
 
     def __repr__(self):
         return f"LayerSpec({self.block!r}, {dict(self.parts)!r})"
@@ -88,6 +91,9 @@ class ScheduleEntry:
     # row of the plan's `stream_offsets` table that is added to the residual stream right before
     # this entry runs (None: nothing is added)
     add_offset: Optional[int] = None
+    # the embedding's output (the stream as it was before the first entry) is added to the stream
+    # right before this entry runs, ahead of `add_offset`
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -1,8 +1,15 @@
 """Arrangements of a layer's parts."""
 from __future__ import annotations
 
+from typing import Dict, Optional
+
+import torch
+
+from ..errors import InvalidError
+from ..kernels import ops
 from ..registry import register_block
-from .base import Block
+from ..weights.loader import TensorSpec
+from .base import Block, CompositeRequest, StateRequest
 from .norm import StreamCast
 
 STREAM_ITSELF = StreamCast()  # what a block whose sublayers read the stream itself has for an entry norm
@@ -52,6 +59,85 @@ class PreNormMixerBlock(Block):
         hidden = self.mixer.forward(x, ctx, cache, residual=hidden)
         ctx.may_defer = False
         return hidden
+
+
+class _ScaledPreNormBlock(Block):
+    """Pre-norm sublayers whose outputs enter the stream under a factor per channel:
+    hidden += mult * scale * sublayer(norm(hidden)), with `scale` a stored vector per sublayer
+    (`layer_scale`; tensors `mixer_scale`, `feed_forward_scale`) and `mult` one number for the model.
+    A sublayer's output stays float32 up to the addition. With `token_shift` the mixer reads
+    h + (h' - h) * shift instead of its norm's output h, h' being the previous token's h (zeros for
+    a sequence's first token; tensor `shift`); the last h of every sequence is state of the layer,
+    kept beside the mixer's own."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, residual_mult: float = 1.0, layer_scale: bool = False,
+                 token_shift: bool = False, **parts):
+        super().__init__(**parts)
+        self.hidden_size, self.residual_mult = int(hidden_size), float(residual_mult)
+        self.layer_scale, self.token_shift = bool(layer_scale), bool(token_shift)
+        self.factors: Dict[str, torch.Tensor] = {}
+        self.shift: Optional[torch.Tensor] = None
+
+    @property
+    def folds_pending_on_entry(self) -> bool:
+        return self.mixer_norm.folds_pending
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        out = {}
+        if self.layer_scale:
+            out.update({role + "_scale": TensorSpec((self.hidden_size,)) for role in ("mixer", "feed_forward")
+                        if role in self.parts})
+        if self.token_shift:
+            out["shift"] = TensorSpec((self.hidden_size,))
+        return out
+
+    def bind(self, weights, runtime) -> None:
+        for role in ("mixer", "feed_forward"):
+            if role in self.parts:
+                scale = weights[role + "_scale"].to(torch.float32) if self.layer_scale else \
+                    torch.ones(self.hidden_size, dtype=torch.float32, device=runtime.device)
+                self.factors[role] = (scale * self.residual_mult).contiguous()
+        if self.token_shift:
+            self.shift = weights["shift"].to(torch.float32).contiguous()
+
+    def cache_request(self):
+        request = self.mixer.cache_request()
+        if not self.token_shift:
+            return request
+        return CompositeRequest((request, StateRequest((1, self.hidden_size), torch.float32)))
+
+    def _mixer_half(self, hidden, ctx, cache):
+        x = self.mixer_norm.forward(hidden, ctx)
+        if self.token_shift:
+            if cache is None or not ctx.entry.writes_cache:
+                raise InvalidError("a layer with token shift keeps state of its own")
+            cache, last = cache
+            x = ops.token_shift(x, self.shift, last.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots)
+        y = self.mixer.forward(x, ctx, cache, residual=None)
+        return ops.scaled_add_(hidden, y, self.factors["mixer"])
+
+
+@register_block("scaled_pre_norm")
+class ScaledPreNormBlock(_ScaledPreNormBlock):
+    """A mixer and a feed-forward, each behind a norm, each added under its factor."""
+
+    def forward(self, hidden, ctx, cache):
+        hidden = self._mixer_half(hidden, ctx, cache)
+        x = self.feed_forward_norm.forward(hidden, ctx)
+        y = self.feed_forward.forward(x, ctx, residual=None)
+        return ops.scaled_add_(hidden, y, self.factors["feed_forward"])
+
+
+@register_block("scaled_pre_norm_mixer")
+class ScaledPreNormMixerBlock(_ScaledPreNormBlock):
+    """The same for a layer without a feed-forward."""
+
+    roles = {"mixer": "mixer", "mixer_norm": "norm"}
+
+    def forward(self, hidden, ctx, cache):
+        return self._mixer_half(hidden, ctx, cache)
 
 
 class _SandwichBlock(Block):

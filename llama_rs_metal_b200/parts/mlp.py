@@ -21,13 +21,15 @@ class GatedMLP(FeedForward):
     (crates/model-runtime/src/execute.rs:251-267). The reference builds SiLU only
     (crates/model-format/src/mlx/config.rs:58-64). Activation "clamped_gate" is the gate of the
     mixture of experts as a dense layer: g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit),
-    down(g sigmoid(alpha g) (u + 1)); gate and up keep their float32 sums up to the activation."""
+    down(g sigmoid(alpha g) (u + 1)); gate and up keep their float32 sums up to the activation.
+    Activation "gelu_tanh": act(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), likewise from
+    float32 sums."""
 
     graph_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu",
                  limit: float = 7.0, alpha: float = 1.702):
-        if activation not in ("silu", "clamped_gate"):
+        if activation not in ("silu", "clamped_gate", "gelu_tanh"):
             raise UnsupportedError(f"feed-forward activation {activation!r}")
         self.activation, self.limit, self.alpha = activation, float(limit), float(alpha)
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
@@ -53,6 +55,9 @@ class GatedMLP(FeedForward):
         if self.activation == "clamped_gate":
             both = self.gate_up(x, out_dtype=torch.float32)
             gated = ops.clamped_gate_mul(both, self.block, self.limit, self.alpha, out_dtype=x.dtype)
+            return self.down(gated, epilogue=ops.ADD, out=residual, ctx=ctx)
+        if self.activation == "gelu_tanh":
+            gated = ops.gelu_tanh_mul(self.gate_up(x, out_dtype=torch.float32), self.block, out_dtype=x.dtype)
             return self.down(gated, epilogue=ops.ADD, out=residual, ctx=ctx)
         if self.block == GATE_BLOCK and self.gate_up.supports_fused_gate(x.dtype):
             gated = self.gate_up(x, epilogue=ops.SILU_GATE)

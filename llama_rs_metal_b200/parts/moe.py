@@ -40,7 +40,10 @@ class MixtureOfExperts(FeedForward):
     outputs of the `keep` best groups can be chosen. `identity` n: the router has n more outputs
     than there are experts; the last n are identity experts without matrices, whose output is the
     layer's input itself (the float32 stream where the block gives it) times the weight. `shared`
-    (a PartSpec of a feed-forward): a part that runs for every token and is added."""
+    (a PartSpec of a feed-forward): a part that runs for every token and is added; with `shared_gate`
+    it is first multiplied by sigmoid(w . x), one number per token (tensor `shared.gate`, [1, hidden],
+    kept and applied in float32). `renormalize_eps` is added to the sum the chosen scores are divided
+    by, `weight_scale` multiplies the weights afterwards."""
 
     graph_safe = True
     ROUTER_ROWS = 256  # up to this many tokens the router always runs as one launch, a CTA per token
@@ -51,7 +54,8 @@ class MixtureOfExperts(FeedForward):
                  activation: str = "clamped_gate", limit: float = 7.0, alpha: float = 1.702,
                  router_bias: bool = True, scoring: str = "softmax_chosen", correction: bool = False,
                  groups: Optional[Tuple[int, int]] = None, renormalize: bool = False, identity: int = 0,
-                 shared: Optional[PartSpec] = None):
+                 shared: Optional[PartSpec] = None, weight_scale: float = 1.0, renormalize_eps: float = 0.0,
+                 shared_gate: bool = False):
         if activation not in ("clamped_gate", "silu"):
             raise UnsupportedError(f"expert activation {activation!r}")
         if scoring not in ("softmax_chosen", "softmax_all"):
@@ -60,6 +64,10 @@ class MixtureOfExperts(FeedForward):
         if num_experts <= 0 or identity < 0 or not 0 < top <= outputs:
             raise InvalidError("the router chooses between 1 and all of the experts")
         count, keep = groups if groups is not None else (1, 1)
+        if (shared_gate and shared is None) or (scoring == "softmax_chosen" and (weight_scale != 1.0 or renormalize_eps)):
+            raise UnsupportedError("a gate needs a shared part; weight scale and epsilon belong to the softmax_all router")
+        self.weight_scale, self.renormalize_eps, self.shared_gate = float(weight_scale), float(renormalize_eps), bool(shared_gate)
+        self.shared_gate_weight: Optional[torch.Tensor] = None
         if scoring == "softmax_chosen" and (correction or groups is not None or identity or renormalize):
             raise UnsupportedError("corrections, groups and identity experts belong to the softmax_all router")
         if count <= 0 or outputs % count or not 0 < keep <= count or top > keep * (outputs // count):
@@ -87,6 +95,8 @@ class MixtureOfExperts(FeedForward):
         if self.shared is not None:
             for own, spec in self.shared.tensors().items():
                 out["shared." + own] = spec
+            if self.shared_gate:
+                out["shared.gate"] = TensorSpec((1, h))
         for e in range(self.num_experts):
             out[f"experts.{e}.gate_proj.weight"] = TensorSpec((f, h))
             out[f"experts.{e}.up_proj.weight"] = TensorSpec((f, h))
@@ -98,9 +108,12 @@ class MixtureOfExperts(FeedForward):
         self.bias = weights["router.bias"].to(torch.float32).contiguous() if self.router_bias else None
         if self.scored:
             correction = weights["router.correction"].to(torch.float32).contiguous() if self.has_correction else None
-            self.scoring = ops.Scoring(correction, self.groups, self.keep, self.renormalize)
+            self.scoring = ops.Scoring(correction, self.groups, self.keep, self.renormalize, self.renormalize_eps,
+                                       self.weight_scale)
         if self.shared is not None:
             self.shared.bind({own: weights["shared." + own] for own in self.shared.tensors()}, runtime)
+            if self.shared_gate:
+                self.shared_gate_weight = weights["shared.gate"].to(torch.float32).reshape(-1).contiguous()
         E, f, h = self.num_experts, self.intermediate_size, self.hidden_size
         self.gate_up = torch.stack([torch.cat([weights[f"experts.{e}.gate_proj.weight"],
                                                weights[f"experts.{e}.up_proj.weight"]]) for e in range(E)]).contiguous()
@@ -131,6 +144,8 @@ class MixtureOfExperts(FeedForward):
             # a block that puts a norm between this part and the stream: the shared part's float32
             # output (or the all-experts product's) is what everything else is added to
             out = self.shared.forward(x, ctx, residual=None) if self.shared is not None else None
+            if self.shared_gate:
+                ops.row_gate_(out, x, self.shared_gate_weight)
             if dense:
                 both = self.gate_up_all(x, out_dtype=torch.float32)
                 y = ops.moe_dense_gate(both, ids, weights, self.num_experts, self.limit, self.alpha, out_dtype=x.dtype,
@@ -143,7 +158,11 @@ class MixtureOfExperts(FeedForward):
             if out is None:
                 out, planes = planes[0], planes[1:]
             return ops.add_planes_(out, planes) if planes.shape[0] else out
-        if self.shared is not None:
+        if self.shared_gate:
+            gated = ops.row_gate_(self.shared.forward(x, ctx, residual=None), x, self.shared_gate_weight)
+            ctx.settle(residual)
+            ops.add_(residual, gated)
+        elif self.shared is not None:
             residual = self.shared.forward(x, ctx, residual=residual)
             ctx.settle(residual)
         if dense:

@@ -17,22 +17,26 @@ class RMSNorm(Norm):
     """y = x / sqrt(mean(x^2) + eps) * (offset + w), statistics in float32
     (crates/metal-backend/src/shaders/elementwise.metal:31-46; no +1 offset for Llama).
     `offset` 1 is for checkpoints that keep a norm's weight as its difference from 1; the sum is made once, in float32, when the
-    weights are bound."""
+    weights are bound. `scalar`: the stored weight is one number (a tensor without dimensions) that
+    multiplies every coordinate; it is spread over the row once, when the weights are bound."""
 
     graph_safe = True
     folds_pending = True
 
-    def __init__(self, size: int, eps: float, offset: float = 0.0):
+    def __init__(self, size: int, eps: float, offset: float = 0.0, scalar: bool = False):
         self.size = size
         self.eps = float(eps)
         self.offset = float(offset)
+        self.scalar = bool(scalar)
         self.weight: Optional[torch.Tensor] = None
 
     def tensors(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,))}
+        return {"weight": TensorSpec(() if self.scalar else (self.size,))}
 
     def bind(self, weights, runtime) -> None:
         weight = weights["weight"]
+        if self.scalar:
+            weight = weight.reshape(1).expand(self.size)
         if self.offset != 0.0:
             weight = weight.to(torch.float32) + self.offset
         self.weight = weight.contiguous()

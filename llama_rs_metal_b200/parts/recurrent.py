@@ -8,6 +8,10 @@ update it token by token and read it out with the query (csrc/recurrent_scan.cu)
 * `gated_delta_rule`: S <- diag(g) S; S <- S + k (b (v - S^T k))^T with decays g per key channel
   and step sizes b computed from the input; q, k, v pass a short causal convolution first.
 
+* `generalized_delta_rule`: S <- diag(g) S - (a * u) (u^T S) + k v^T with a decay g and a removal rate
+  a per key channel, both computed from the input, u the unit key, both terms reading the old S
+  (csrc/general_delta.cu prepares its inputs).
+
 A third keeps one number per channel (csrc/gated_recurrence.cu):
 
 * `gated_linear_recurrence`: S <- a S + sqrt(1 - a^2) (i u) with a decay a and an input gate i
@@ -185,6 +189,72 @@ class GatedDeltaRule(Mixer):
         o = ops.linear_state_scan(q, k, v, state.state, ctx.cu_seqlens, ctx.slots, g=g, beta=beta)
         mixed = ops.head_norm_gate(o, self.eps, projected.dtype, weight=self.norm_weight, gate=both,
                                    gate_column=H * d, gate_act=ops.GATE_SIGMOID, out_scale=self.output_scale)
+        return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
+
+
+@register_mixer("generalized_delta_rule")
+class GeneralizedDeltaRule(Mixer):
+    """r = W_r x, k = W_k x (heads x head_dim), v = W_v x (heads x value_dim). Per head and key channel
+    a decay g = exp(-decay_scale * sigmoid(W_d2 tanh(W_d1 x) + d_bias)) and a removal rate
+    a = sigmoid(W_a x + a_bias); with the unit key u = k / sqrt(sum k^2 + unit_eps) of each head,
+        S <- diag(g) S - (a * u) (u^T S) + k v^T    (both terms read the state before the token),
+        o = S^T r    (the state after it).
+    o is divided by its root mean square over value_dim (`eps`), multiplied by a weight over all heads'
+    columns and by sigmoid(W_g x), then projected. The inner rank of the decay's low-rank product is
+    the checkpoint's (`decay_rank` None) unless given. Everything behind the projections (the tanh is
+    rounded to the activation type where it enters the second product) is float32.
+    State: S [heads, head_dim, value_dim] in float32."""
+
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, value_dim: int, eps: float,
+                 decay_scale: float, decay_rank: Optional[int] = None, unit_eps: float = 1e-6):
+        if min(num_heads, head_dim, value_dim) <= 0 or not decay_scale > 0:
+            raise InvalidError("generalized delta rule: sizes and the decay's scale must be positive")
+        self.hidden_size, self.num_heads, self.head_dim, self.value_dim = hidden_size, num_heads, head_dim, value_dim
+        self.eps, self.decay_scale, self.decay_rank, self.unit_eps = float(eps), float(decay_scale), decay_rank, float(unit_eps)
+        self.fused: Optional[LinearWeight] = None
+        self.high: Optional[LinearWeight] = None
+        self.out: Optional[LinearWeight] = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        H, d, dv, h = self.num_heads, self.head_dim, self.value_dim, self.hidden_size
+        return {"r_proj.weight": TensorSpec((H * d, h)), "k_proj.weight": TensorSpec((H * d, h)),
+                "v_proj.weight": TensorSpec((H * dv, h)), "g_proj.weight": TensorSpec((H * dv, h)),
+                "a_proj.weight": TensorSpec((H * d, h)), "a_proj.bias": TensorSpec((H * d,)),
+                "d_down.weight": TensorSpec((self.decay_rank, h)), "d_up.weight": TensorSpec((H * d, self.decay_rank)),
+                "d_bias": TensorSpec((H * d,)), "norm.weight": TensorSpec((H * dv,)),
+                "o_proj.weight": TensorSpec((h, H * dv))}
+
+    def bind(self, weights, runtime) -> None:
+        f32 = torch.float32
+        down, up = weights["d_down.weight"], weights["d_up.weight"]
+        if up.shape[1] != down.shape[0]:
+            raise InvalidError("generalized delta rule: the two halves of the decay's product disagree on its rank")
+        # r | k | v | g | a | the decay's first product, in one product
+        self.fused = LinearWeight(torch.cat([weights[n + "_proj.weight"] for n in "rkvga"] + [down], dim=0))
+        self.rank = down.shape[0]
+        self.high = LinearWeight(up)
+        self.out = LinearWeight(weights["o_proj.weight"])
+        self.a_bias = weights["a_proj.bias"].to(f32).contiguous()
+        self.d_bias = weights["d_bias"].to(f32).contiguous()
+        self.norm_weight = weights["norm.weight"].to(f32).contiguous()
+
+    def cache_request(self):
+        return StateRequest((self.num_heads, self.head_dim, self.value_dim), torch.float32)
+
+    def forward(self, x, ctx, cache, residual):
+        _needs_own_state(ctx)
+        H, d, dv = self.num_heads, self.head_dim, self.value_dim
+        projected = self.fused(x, out_dtype=torch.float32)               # [T, r | k | v | g | a | low], float32
+        at_v, at_g, at_a, at_low = 2 * H * d, 2 * H * d + H * dv, 2 * H * d + 2 * H * dv, 3 * H * d + 2 * H * dv
+        inner = ops.tanh_columns(projected, at_low, self.rank, x.dtype)
+        z = self.high(inner, out_dtype=torch.float32)                    # [T, H d], float32
+        r, k, v, g, look, put = ops.general_delta_prepare(projected, 0, H * d, at_v, at_a, z, self.d_bias, self.a_bias,
+                                                          self.decay_scale, self.unit_eps, H, d, dv)
+        o = ops.general_delta_scan(r, k, v, g, look, put, cache.state, ctx.cu_seqlens, ctx.slots)
+        mixed = ops.head_norm_gate(o, self.eps, x.dtype, weight=self.norm_weight, gate=projected, gate_column=at_g,
+                                   gate_act=ops.GATE_SIGMOID)
         return self.out(mixed, epilogue=ops.ADD, out=residual, ctx=ctx)
 
 

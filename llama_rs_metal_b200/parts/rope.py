@@ -49,6 +49,7 @@ class RotaryEmbedding(PositionEncoding):
         self.original = int(original_max_position_embeddings)
         self.adjacent_pairs = bool(adjacent_pairs)
         self.inv_freq: Optional[torch.Tensor] = None
+        self.inv_freq64: Optional[torch.Tensor] = None
 
     def inverse_frequencies(self) -> List[float]:
         out = []
@@ -79,6 +80,8 @@ class RotaryEmbedding(PositionEncoding):
             _shared_frequencies[key] = torch.tensor(frequencies, dtype=torch.float64) \
                 .to(torch.float32).to(runtime.device)
         self.inv_freq = _shared_frequencies[key]
+        # the same in double precision, for kernels that form the angle in double precision
+        self.inv_freq64 = torch.tensor(frequencies, dtype=torch.float64).to(runtime.device)
 
     def head_permutation(self) -> Optional[List[int]]:
         if not self.adjacent_pairs:

@@ -38,7 +38,7 @@ def random_tensors(wanted: Mapping[str, TensorSpec], seed: int, std: float = 0.0
         if any(n is None for n in spec.shape):
             raise ValueError(f"{name}: a dimension is left to the checkpoint; random weights need it in the configuration")
         gen = _generator(seed, name, device)
-        vector = is_vector(name, spec) if is_vector else len(spec.shape) == 1
+        vector = is_vector(name, spec) if is_vector else len(spec.shape) <= 1
         if spec.kind == "integer":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32, device=device)
         elif vector:
