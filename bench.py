@@ -273,13 +273,33 @@ def norevik_shape(width, heads, ff, experts, top, layers, vocab=32768):
                 layers=[dict(kinds[i % 3]) for i in range(layers)])
 
 
+def tarupel_shape(width, heads, kv_heads, ff, experts, top, window, layers, vocab=32768):
+    """A Tarupel configuration with layers of a real model's widths: a generalized delta rule (heads
+    of 64), chunked attention with short convolutions (head size 128, a quarter of it rotated, chunks
+    of `window`) and windowed attention with row norms (head size 128) in turn; behind each a mixture
+    of `experts` experts in four groups of which three are kept, `top` chosen, and a gated shared
+    expert as wide as one expert. The first two layers loop twice."""
+    d = 128
+    moe = dict(kind="moe", expert=dict(ff=ff), shared=dict(ff=ff),
+               router=dict(experts=experts, top=top, scale=1.5, groups=dict(count=4, keep=3)))
+    kinds = [
+        dict(type="general_delta", mixer=dict(heads=width // 64, dim=64, decay_rank=64), mlp=moe),
+        dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=d, vdim=d, scale=d ** -0.5, conv=4,
+                                          rot=dict(dims=32, base=50000.0), mask=dict(size=window)), mlp=moe),
+        dict(type="attention_2", mixer=dict(heads=heads, kv_heads=kv_heads, dim=d, vdim=d, scale=d ** -0.5,
+                                            rot=dict(dims=32, base=1000000.0), mask=dict(size=window)), mlp=moe),
+    ]
+    return dict(architecture="Tarupel", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
+                residual_mult=0.5, layers=[dict(kinds[i % 3]) for i in range(layers)], loop=dict(start=0, stop=2, times=2))
+
+
 def design_bench(args) -> int:
-    """Prefill and decode throughput of the Kikalix, the Pibuvik or the Norevik design at a few
+    """Prefill and decode throughput of the Kikalix, the Pibuvik, the Norevik or the Tarupel design at a few
     layer sizes, beside an existing decoder at equal size: Kikalix and Pibuvik beside Llama (the same
     width, head geometry, vocabulary and number of layer runs; its feed-forward as wide as the
-    experts a token uses, or as the dense one), Norevik beside Kikalix, the closest of the designs
-    (state mixers on the same scan, the same experts: equal width, heads, experts, chosen experts,
-    expert width, vocabulary and layer runs). Random weights, one GPU, bfloat16."""
+    experts a token uses, or as the dense one), Norevik and Tarupel beside Kikalix, the closest of the
+    designs (state mixers on the same scan, the same experts, a looped run: equal width, heads, experts,
+    chosen experts, expert width, vocabulary and layer runs). Random weights, one GPU, bfloat16."""
     if args.profile:
         os.environ["LRM_PROFILE"] = "1"
     import numpy as np
@@ -351,6 +371,13 @@ def design_bench(args) -> int:
             twin, twin_name = kikalix_shape(width, heads, kv_heads, ff, experts, top, window, layers), "kikalix_equal_size"
             shape = dict(width=width, heads=heads, expert_ff=ff, shared_ff=ff, experts=experts, identity=2, top=top,
                          state_heads=width // 64, state=128, kv_rank=512, layer_runs=runs)
+        elif args.design == "tarupel":
+            width, heads, kv_heads, ff, experts, top, window, layers = DESIGN_SIZES[size]
+            runs, norm_mean = layers + 2, 1.0
+            config = tarupel_shape(width, heads, kv_heads, ff, experts, top, window, layers)
+            twin, twin_name = kikalix_shape(width, heads, kv_heads, ff, experts, top, window, layers), "kikalix_equal_size"
+            shape = dict(width=width, heads=heads, kv_heads=kv_heads, head_dim=128, expert_ff=ff, shared_ff=ff,
+                         experts=experts, top=top, state_heads=width // 64, window=window, layer_runs=runs)
         elif args.design == "pibuvik":
             width, heads, kv_heads, ff, kv_rank, window, layers = PIBUVIK_SIZES[size]
             config = pibuvik_shape(width, heads, kv_heads, ff, kv_rank, window, layers)
@@ -367,7 +394,7 @@ def design_bench(args) -> int:
         row = {args.design: measure(model, config["vocab"], f"{design_name} {size}")}
         del model
         torch.cuda.empty_cache()
-        if args.design == "norevik":
+        if args.design in ("norevik", "tarupel"):
             model = engine.random(twin, seed=0, std=0.02, norm_mean=0.0)
         else:
             twin = llama(width, twin_ff, runs, heads, kv_heads, 128, 8.0, False)
@@ -379,7 +406,7 @@ def design_bench(args) -> int:
         row["shape"] = shape
         out[size] = row
     print(json.dumps({"metric": f"prefill tok/s (one {prompt}-token prompt) and decode tok/s (batch {batch} at "
-                                f"{prompt} tokens), {design_name} beside {'Kikalix' if args.design == 'norevik' else 'Llama'} at equal size",
+                                f"{prompt} tokens), {design_name} beside {'Kikalix' if args.design in ('norevik', 'tarupel') else 'Llama'} at equal size",
                       "dtype": "bf16", "data": "synthetic token ids, random-init weights", "n_gpus": 1,
                       "decode_steps": steps, "peaks": peak_source, "cuda_graph": not args.profile, "sizes": out}))
     return 0
@@ -412,7 +439,7 @@ def main() -> int:
     parser.add_argument("--profile", action="store_true",
                         help="time every kernel launch (LRM_PROFILE=1) and print the table to stderr; the "
                              "line's numbers are then those of unfused, uncaptured launches")
-    parser.add_argument("--design", choices=["kikalix", "pibuvik", "norevik"], default=None,
+    parser.add_argument("--design", choices=["kikalix", "pibuvik", "norevik", "tarupel"], default=None,
                         help="instead of the default workload: prefill and decode throughput of this design at "
                              "a few layer sizes beside an existing decoder at equal size (see design_bench)")
     parser.add_argument("--design-size", choices=sorted(DESIGN_SIZES), default=None,

@@ -7,7 +7,8 @@
 A general_delta mixer: heads, dim (and, for random weights only, decay_rank: the checkpoint's
 tensors give it otherwise). An attention mixer: heads, kv_heads, dim, vdim, scale, conv (taps),
 rot {dims, base}, mask {size} (the chunk). An attention_2 mixer: heads, kv_heads, dim, vdim, scale,
-rot {dims, base}, mask {size} (the window). A feed-forward is {"kind": "dense", "ff"} or {"kind":
+rot {dims, base}, mask {size} (the window); without rot nothing is rotated, without mask every
+earlier key is seen. A feed-forward is {"kind": "dense", "ff"} or {"kind":
 "moe", "expert": {"ff"}, "router": {"experts", "top", "scale", "groups": {"count", "keep"}}, "shared":
 {"ff"}}; scale, groups and shared may be absent, and so may loop, embedding and residual_mult.
 Every size and every constant that can differ between models comes from here.
@@ -52,7 +53,7 @@ class MaskedAttentionConfig:
     scale: float
     rot_dims: int
     rot_base: float
-    span: int
+    span: Optional[int]
     conv: Optional[int] = None
 
     @classmethod
@@ -60,19 +61,21 @@ class MaskedAttentionConfig:
         heads, kv_heads, dim, vdim = (_positive(m, k, where) for k in ("heads", "kv_heads", "dim", "vdim"))
         if heads % kv_heads:
             raise InvalidError(f"config.{where}heads must be a multiple of kv_heads")
-        rot = _table(m, "rot", where)
+        rot = m.get("rot") if isinstance(m.get("rot"), Mapping) else {}
         dims, base = read_int(rot, "dims", 0), 10000.0
         if dims:
             base = _real(rot, "base", where + "rot.")
         if dims % 2 or dims > dim or base <= 0:
             raise InvalidError(f"config.{where}rot: dims must be even and at most dim, base positive")
-        span = _positive(_table(m, "mask", where), "size", where + "mask.")
+        span = _positive(m["mask"], "size", where + "mask.") if isinstance(m.get("mask"), Mapping) else None
         conv = _positive(m, "conv", where) if with_conv else None
         return cls(heads, kv_heads, dim, vdim, _real(m, "scale", where), dims, base, span, conv)
 
     def to_dict(self) -> dict:
         out = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-               "rot": {"dims": self.rot_dims, "base": self.rot_base}, "mask": {"size": self.span}}
+               "rot": {"dims": self.rot_dims, "base": self.rot_base}}
+        if self.span is not None:
+            out["mask"] = {"size": self.span}
         if self.conv is not None:
             out["conv"] = self.conv
         return out

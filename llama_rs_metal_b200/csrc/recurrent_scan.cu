@@ -32,7 +32,7 @@
 namespace {
 
 constexpr int kScanThreads = 128;
-constexpr int kChunk = 16;
+constexpr int kChunk = 16;  // tokens per stage, halved while two stages do not fit the shared memory
 
 __device__ __forceinline__ void scan_cp_async(float* dst, const float* src, bool valid, bool wide) {
   const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(dst));
@@ -55,7 +55,7 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
     const float* __restrict__ g, const float* __restrict__ head_decay, const float* __restrict__ beta,
     const float* __restrict__ look, const float* __restrict__ put,
     float* __restrict__ state, float* __restrict__ out, const int* __restrict__ cu_seqlens,
-    const int* __restrict__ slots, int H, int KH, int d, int dv, int P) {
+    const int* __restrict__ slots, int H, int KH, int d, int dv, int P, int chunk) {
   extern __shared__ __align__(16) float smem[];
   constexpr bool DELTA = MODE == 1;
   constexpr bool GEN = MODE == 3;
@@ -64,7 +64,7 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
   const int TS = P * RS, COLS = kScanThreads / P;
   const int VS = (COLS + 3) & ~3;                       // v of a token, padded to whole 16 bytes
   const int TOKEN = NR * TS + VS + 4;                   // q | k | (g) | (look | put) | v | beta
-  const int STAGE = kChunk * TOKEN;
+  const int STAGE = chunk * TOKEN;
 
   const int tid = threadIdx.x, pidx = tid % P, jl = tid / P;
   const int h = blockIdx.y, b = blockIdx.z, kh = h / (H / KH);
@@ -86,7 +86,7 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
 
   auto issue = [&](int c0, int stage) {
     float* base = smem + stage * STAGE;
-    const int cn = min(kChunk, n - c0);
+    const int cn = min(chunk, n - c0);
     const int per_token = ROWS * P / step;  // granules of a q (k, g) row, padding rows included
     for (int idx = tid; idx < cn * per_token; idx += kScanThreads) {
       const int c = idx / per_token, r = (idx % per_token) * step;
@@ -116,10 +116,10 @@ __global__ __launch_bounds__(kScanThreads) void linear_scan_kernel(
   };
 
   if (n > 0) issue(0, 0);
-  for (int c0 = 0, it = 0; c0 < n; c0 += kChunk, ++it) {
-    const int cn = min(kChunk, n - c0);
-    if (c0 + kChunk < n) {
-      issue(c0 + kChunk, (it + 1) & 1);
+  for (int c0 = 0, it = 0; c0 < n; c0 += chunk, ++it) {
+    const int cn = min(chunk, n - c0);
+    if (c0 + chunk < n) {
+      issue(c0 + chunk, (it + 1) & 1);
       asm volatile("cp.async.wait_group 1;\n" ::);
     } else {
       asm volatile("cp.async.wait_group 0;\n" ::);
@@ -197,7 +197,10 @@ int launch_scan(const float* q, const float* k, const float* v, const float* g, 
                 int seqs, int H, int KH, int d, int dv, int P, cudaStream_t stream) {
   constexpr int NR = MODE == 1 ? 3 : MODE == 3 ? 5 : 2;
   const int COLS = kScanThreads / P, TS = P * (ROWS + 4), VS = (COLS + 3) & ~3;
-  const size_t bytes = sizeof(float) * 2 * kChunk * (static_cast<size_t>(NR) * TS + VS + 4);
+  int chunk = kChunk;
+  while (chunk > 1 && sizeof(float) * 2 * chunk * (static_cast<size_t>(NR) * TS + VS + 4) > 200 * 1024) chunk >>= 1;
+  const size_t bytes = sizeof(float) * 2 * chunk * (static_cast<size_t>(NR) * TS + VS + 4);
+  if (bytes > 200 * 1024) return LRM_UNSUPPORTED;
   static bool raised = false;  // per instantiation
   if (bytes > 48 * 1024 && !raised) {
     cudaError_t e = cudaFuncSetAttribute(linear_scan_kernel<ROWS, MODE>,
@@ -207,7 +210,7 @@ int launch_scan(const float* q, const float* k, const float* v, const float* g, 
   }
   const dim3 grid((dv + COLS - 1) / COLS, H, seqs);
   LRM_LAUNCH((linear_scan_kernel<ROWS, MODE>), grid, kScanThreads, bytes, stream, q, k, v, g, head_decay, beta,
-             look, put, state, out, cu_seqlens, slots, H, KH, d, dv, P);
+             look, put, state, out, cu_seqlens, slots, H, KH, d, dv, P, chunk);
   return 0;
 }
 

@@ -7,10 +7,11 @@ namespace {
 // out[t, c] = h[t, c] + (h[t - 1, c] - h[t, c]) * mix[c], with the previous token's row as it was
 // before this replacement; for a sequence's first token of the step it comes from `last`
 // [slots, width] (float32; zeros at the start of a sequence), and a sequence of padding (slot < 0)
-// has zeros there. One CTA per token. The caller rewrites `last` afterwards (conv_tail_update with
-// two taps keeps exactly this row).
+// has zeros there. One CTA per token. The thread that read last[slot, c] for a sequence's first
+// token then writes the sequence's newest h there (the row of its last token of this step), so
+// `last` is up to date when the kernel ends and nobody reads an entry after it was rewritten.
 template <typename A>
-__global__ void token_shift_kernel(const A* h, const float* __restrict__ mix, const float* last, A* __restrict__ out,
+__global__ void token_shift_kernel(const A* h, const float* __restrict__ mix, float* last, A* __restrict__ out,
                                    const int* __restrict__ cu_seqlens, const int* __restrict__ seq_of_token,
                                    const int* __restrict__ slots, int width) {
   pdl_trigger();
@@ -19,12 +20,36 @@ __global__ void token_shift_kernel(const A* h, const float* __restrict__ mix, co
   const int b = seq_of_token[t], local = t - cu_seqlens[b], slot = slots[b];
   const A* row = h + static_cast<size_t>(t) * width;
   const A* before = local > 0 ? row - width : nullptr;
-  const float* kept = (local == 0 && slot >= 0) ? last + static_cast<size_t>(slot) * width : nullptr;
+  float* kept = (local == 0 && slot >= 0) ? last + static_cast<size_t>(slot) * width : nullptr;
+  const A* newest = h + static_cast<size_t>(cu_seqlens[b + 1] - 1) * width;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float x = to_f32(row[c]);
     const float p = before != nullptr ? to_f32(before[c]) : kept != nullptr ? kept[c] : 0.f;
     out[static_cast<size_t>(t) * width + c] = from_f32<A>(fmaf(p - x, mix[c], x));
+    if (kept != nullptr) kept[c] = to_f32(newest[c]);
   }
+}
+
+// x[t, :] += factor * y[t, :], then out[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w in the
+// activation type: a sublayer's output enters the stream and the updated row goes through the next
+// sublayer's norm in the same pass. One CTA per row; a thread reads back only what it wrote itself.
+template <typename W, typename O>
+__global__ void scaled_add_norm_kernel(float* x, const float* y, const float* __restrict__ factor,
+                                       const W* __restrict__ w, float eps, O* __restrict__ out, int width) {
+  __shared__ float scratch[32];
+  pdl_trigger();
+  pdl_wait();
+  float* row = x + static_cast<size_t>(blockIdx.x) * width;
+  const float* add = y + static_cast<size_t>(blockIdx.x) * width;
+  O* dst = out + static_cast<size_t>(blockIdx.x) * width;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = fmaf(factor[c], add[c], row[c]);
+    row[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / static_cast<float>(width) + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = from_f32<O>((row[c] * inv) * to_f32(w[c]));
 }
 
 // x[t, c] += factor[c] * y[t, c]: a sublayer's float32 output enters the float32 stream under a
@@ -54,7 +79,7 @@ __global__ void row_gate_kernel(float* y, const A* x, const float* __restrict__ 
 
 }  // namespace
 
-LRM_API int lrm_token_shift(const void* h, int dtype, const float* mix, const float* last, void* out,
+LRM_API int lrm_token_shift(const void* h, int dtype, const float* mix, float* last, void* out,
                             const int* cu_seqlens, const int* seq_of_token, const int* slots, int tokens, int width,
                             cudaStream_t stream) {
   if (tokens <= 0) return 0;
@@ -77,6 +102,31 @@ LRM_API int lrm_scaled_add(float* x, const float* y, const float* factor, long l
   if (x == nullptr || y == nullptr || factor == nullptr || width <= 0) return LRM_BAD_ARGUMENT;
   const size_t n = static_cast<size_t>(rows) * width;
   LRM_LAUNCH(scaled_add_kernel, static_cast<unsigned>((n + 255) / 256), 256, 0, stream, x, y, factor, width, n);
+  return 0;
+}
+
+// w has w_dtype, out out_dtype (float32 or bfloat16 each).
+LRM_API int lrm_scaled_add_norm(float* x, const float* y, const float* factor, const void* w, int w_dtype, float eps,
+                                void* out, int out_dtype, long long rows, int width, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (x == nullptr || y == nullptr || factor == nullptr || w == nullptr || out == nullptr || width <= 0)
+    return LRM_BAD_ARGUMENT;
+  const unsigned grid = static_cast<unsigned>(rows);
+  const int threads = width >= 1024 ? 256 : width >= 256 ? 128 : 64;
+#define LRM_SAN(WT, OT)                                                                                          \
+  LRM_LAUNCH((scaled_add_norm_kernel<WT, OT>), grid, threads, 0, stream, x, y, factor, static_cast<const WT*>(w), eps, \
+             static_cast<OT*>(out), width)
+  if (w_dtype == LRM_F32 && out_dtype == LRM_F32)
+    LRM_SAN(float, float);
+  else if (w_dtype == LRM_BF16 && out_dtype == LRM_BF16)
+    LRM_SAN(__nv_bfloat16, __nv_bfloat16);
+  else if (w_dtype == LRM_F32 && out_dtype == LRM_BF16)
+    LRM_SAN(float, __nv_bfloat16);
+  else if (w_dtype == LRM_BF16 && out_dtype == LRM_F32)
+    LRM_SAN(__nv_bfloat16, float);
+  else
+    return LRM_BAD_ARGUMENT;
+#undef LRM_SAN
   return 0;
 }
 

@@ -348,7 +348,7 @@ def token_shift(h: torch.Tensor, mix: torch.Tensor, last: torch.Tensor, cu_seqle
                 seq_of_token: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
     """h[t] + (h[t-1] - h[t]) * mix per channel, h [T, W] packed sequences; the row before a sequence's
     first token of the step is last[slot] (float32 [slots, 1, W]: the sequence's previous h, zeros at
-    its start). `last` is then rewritten with every sequence's newest row of h."""
+    its start). The kernel also rewrites `last` with every sequence's newest row of h."""
     _check(h, "h", dims=2)
     _check(mix, "mix", torch.float32, 1)
     _check(last, "last", torch.float32, 3)
@@ -360,7 +360,6 @@ def token_shift(h: torch.Tensor, mix: torch.Tensor, last: torch.Tensor, cu_seqle
     out = _activation(T, W, h.dtype, h.device)
     _done(_lib().lrm_token_shift(_ptr(h), _code(h.dtype), _ptr(mix), _ptr(last), _ptr(out), _ptr(cu_seqlens),
                                  _ptr(seq_of_token), _ptr(slots), T, W, _stream()), "token_shift")
-    conv_tail_update_(h, 0, W, 2, last, cu_seqlens, slots)
     return out
 
 
@@ -374,6 +373,23 @@ def scaled_add_(x: torch.Tensor, y: torch.Tensor, factor: torch.Tensor) -> torch
     _done(_lib().lrm_scaled_add(_ptr(x), _ptr(y), _ptr(factor), ctypes.c_longlong(x.shape[0]), x.shape[1], _stream()),
           "scaled_add_")
     return x
+
+
+def scaled_add_norm_(x: torch.Tensor, y: torch.Tensor, factor: torch.Tensor, weight: torch.Tensor, eps: float,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """x[t, :] += factor * y[t, :] (all float32), and in the same pass the updated rows' RMS norm,
+    x / sqrt(mean(x^2) + eps) * weight -> [T, W] in `out_dtype`."""
+    _check(x, "x", torch.float32, 2)
+    _check(y, "y", torch.float32, 2)
+    _check(factor, "factor", torch.float32, 1)
+    _check(weight, "weight", dims=1)
+    if x.shape != y.shape or factor.numel() != x.shape[1] or weight.numel() != x.shape[1]:
+        raise InvalidError("scaled_add_norm_: shapes do not agree")
+    out = _activation(x.shape[0], x.shape[1], out_dtype, x.device)
+    _done(_lib().lrm_scaled_add_norm(_ptr(x), _ptr(y), _ptr(factor), _ptr(weight), _code(weight.dtype),
+                                     ctypes.c_float(eps), _ptr(out), _code(out_dtype), ctypes.c_longlong(x.shape[0]),
+                                     x.shape[1], _stream()), "scaled_add_norm_")
+    return out
 
 
 def row_gate_(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:

@@ -143,6 +143,24 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
     "lrm_moe_route_scored": lambda a: (_v(a[4]) * (_v(a[5]) * 4.0 + _v(a[6]) * 8.0), 0),
     "lrm_moe_identity_add": lambda a: (_v(a[5]) * _v(a[6]) * (8.0 + _ELEM[_v(a[2])]), 0),
     "lrm_sample_gumbel_rows": lambda a: (4.0 * _v(a[4]) * _v(a[5]), 0),
+    # the generalized delta rule: the states read and written once, five rows of d and two of dv per
+    # token and head in float32; per token and state element a decay, three sums and two updates
+    "lrm_general_delta_scan": lambda a: (
+        8.0 * _v(a[10]) * _v(a[11]) * _v(a[12]) * _v(a[13])
+        + 4.0 * hints["tokens"] * _v(a[11]) * (5 * _v(a[12]) + 2 * _v(a[13])),
+        hints["tokens"] * _v(a[11]) * _v(a[12]) * _v(a[13]) * 9.0),
+    "lrm_general_delta_prepare": lambda a: (
+        _v(a[18]) * _v(a[19]) * ((3 * _v(a[20]) + _v(a[21])) * _ELEM[_v(a[1])] + 4.0 * (6 * _v(a[20]) + _v(a[21]))), 0),
+    # the shaped split: the projection row read (taps times, from cache), q, k, v written, k and v again into the cache
+    "lrm_shaped_qkv_store": lambda a: (
+        _v(a[25]) * ((_v(a[26]) * _v(a[28]) + _v(a[27]) * (_v(a[28]) + _v(a[29]))) * (_ELEM[_v(a[1])] + _ELEM[_v(a[24])])
+                     + _v(a[27]) * (_v(a[28]) + _v(a[29])) * _ELEM[_v(a[24])]),
+        2.0 * _v(a[25]) * (_v(a[26]) * _v(a[28]) + _v(a[27]) * (_v(a[28]) + _v(a[29]))) * max(1, _v(a[4]))),
+    "lrm_token_shift": lambda a: (_v(a[8]) * _v(a[9]) * 2.0 * _ELEM[_v(a[1])], 0),
+    "lrm_scaled_add": lambda a: (12.0 * _v(a[3]) * _v(a[4]), 0),
+    "lrm_row_gate": lambda a: (_v(a[4]) * (_v(a[5]) * _ELEM[_v(a[2])] + 8.0 * _v(a[6])), 0),
+    "lrm_gelu_tanh_mul": lambda a: (_v(a[4]) * _v(a[5]) * (2.0 * _ELEM[_v(a[1])] + _ELEM[_v(a[3])]), 0),
+    "lrm_tanh_columns": lambda a: (_v(a[5]) * _v(a[6]) * (_ELEM[_v(a[1])] + _ELEM[_v(a[4])]), 0),
 }
 # entry points that only answer questions and launch nothing
 _QUERIES = ("_supports", "_ctas_per_sm", "_slices", "_pieces", "_resident", "_floats", "_error", "_room", "lrm_set_pdl", "lrm_set_norm_ranks", "lrm_pick_pieces", "lrm_linear_state_scan_rows")

@@ -68,7 +68,9 @@ class _ScaledPreNormBlock(Block):
     A sublayer's output stays float32 up to the addition. With `token_shift` the mixer reads
     h + (h' - h) * shift instead of its norm's output h, h' being the previous token's h (zeros for
     a sequence's first token; tensor `shift`); the last h of every sequence is state of the layer,
-    kept beside the mixer's own."""
+    kept beside the mixer's own. The pass that adds a sublayer's output also applies the norm that
+    comes next (the feed-forward's, or the next block's first norm when that block takes it, handed
+    over through StepContext.normed)."""
 
     graph_safe = True
 
@@ -108,15 +110,29 @@ class _ScaledPreNormBlock(Block):
             return request
         return CompositeRequest((request, StateRequest((1, self.hidden_size), torch.float32)))
 
-    def _mixer_half(self, hidden, ctx, cache):
-        x = self.mixer_norm.forward(hidden, ctx)
+    @property
+    def entry_norm(self):
+        return self.mixer_norm
+
+    def _add(self, hidden, y, role, then, ctx):
+        """hidden += factor * y; returns then.forward(hidden) of the updated stream (None without `then`)."""
+        from .norm import RMSNorm
+        if isinstance(then, RMSNorm) and then.weight is not None and ctx.pending is None:
+            return ops.scaled_add_norm_(hidden, y, self.factors[role], then.weight, then.eps, ctx.runtime.dtype)
+        ops.scaled_add_(hidden, y, self.factors[role])
+        return then.forward(hidden, ctx) if then is not None else None
+
+    def _mixer_half(self, hidden, ctx, cache, then):
+        x = ctx.take_normed(self.mixer_norm)
+        if x is None:
+            x = self.mixer_norm.forward(hidden, ctx)
         if self.token_shift:
             if cache is None or not ctx.entry.writes_cache:
                 raise InvalidError("a layer with token shift keeps state of its own")
             cache, last = cache
             x = ops.token_shift(x, self.shift, last.state, ctx.cu_seqlens, ctx.seq_of_token, ctx.slots)
         y = self.mixer.forward(x, ctx, cache, residual=None)
-        return ops.scaled_add_(hidden, y, self.factors["mixer"])
+        return self._add(hidden, y, "mixer", then, ctx)
 
 
 @register_block("scaled_pre_norm")
@@ -124,10 +140,12 @@ class ScaledPreNormBlock(_ScaledPreNormBlock):
     """A mixer and a feed-forward, each behind a norm, each added under its factor."""
 
     def forward(self, hidden, ctx, cache):
-        hidden = self._mixer_half(hidden, ctx, cache)
-        x = self.feed_forward_norm.forward(hidden, ctx)
+        following = ctx.next_entry_norm
+        x = self._mixer_half(hidden, ctx, cache, self.feed_forward_norm)
         y = self.feed_forward.forward(x, ctx, residual=None)
-        return ops.scaled_add_(hidden, y, self.factors["feed_forward"])
+        normed = self._add(hidden, y, "feed_forward", following, ctx)
+        ctx.normed = (following, normed) if following is not None else None
+        return hidden
 
 
 @register_block("scaled_pre_norm_mixer")
@@ -137,7 +155,10 @@ class ScaledPreNormMixerBlock(_ScaledPreNormBlock):
     roles = {"mixer": "mixer", "mixer_norm": "norm"}
 
     def forward(self, hidden, ctx, cache):
-        return self._mixer_half(hidden, ctx, cache)
+        following = ctx.next_entry_norm
+        normed = self._mixer_half(hidden, ctx, cache, following)
+        ctx.normed = (following, normed) if following is not None else None
+        return hidden
 
 
 class _SandwichBlock(Block):

@@ -144,7 +144,7 @@ def write_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dic
         t = tensors[name].detach().contiguous().cpu()
         if t.dtype not in _NAMES:
             raise UnsupportedError(f"{name}: dtype {t.dtype} cannot be stored")
-        raw = t.view(torch.uint8).reshape(-1).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""  # (a tensor without dimensions too)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape),
                         "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)

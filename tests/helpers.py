@@ -303,6 +303,115 @@ def make_norevik_dir(path, name, dtype=torch.bfloat16, edit=None, steady_routing
     return write_model_folder(path, config.to_dict(), tensors, spec["seed"])
 
 
+def _delta(heads, dim, rank):
+    return dict(heads=heads, dim=dim, decay_rank=rank)
+
+
+def _masked(heads, kv_heads, dim, vdim, scale, rot_dims, base, size, conv=None):
+    out = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, rot=dict(dims=rot_dims, base=base),
+               mask=dict(size=size))
+    if conv is not None:
+        out["conv"] = conv
+    return out
+
+
+def _scored_experts(ff, experts, top, scale=None, groups=None, shared=None):
+    router = dict(experts=experts, top=top)
+    if scale is not None:
+        router["scale"] = scale
+    if groups is not None:
+        router["groups"] = dict(count=groups[0], keep=groups[1])
+    out = dict(kind="moe", expert=dict(ff=ff), router=router)
+    if shared is not None:
+        out["shared"] = dict(ff=shared)
+    return out
+
+
+# Three tiny Tarupel configurations. Between them: odd sizes everywhere (T1), a loop in the middle
+# three times, at the start, and none; head sizes 64 and 128 so that bfloat16 takes the tensor-core
+# attention kernels (T2) and others that take the row-wise one; values wider and narrower than keys;
+# one key head, as many as query heads, and groups; chunks and windows shorter than a page, of one
+# page, and longer; a window and a chunk of one position; one tap and five; rotation of the whole
+# head and of a part; routers with and without groups, with every expert chosen, without a shared
+# expert, without a scale; layers without a feed-forward; residual factors 1 and others.
+TARUPEL = {
+    "T1": dict(
+        config=dict(architecture="Tarupel", vocab=211, width=72, norm=dict(eps=1e-6), embedding=dict(scale=3.0),
+                    residual_mult=0.7, loop=dict(start=1, stop=3, times=3), layers=[
+            dict(type="attention_2", mixer=_masked(3, 1, 12, 20, 0.3, 6, 100.0, 7), mlp=dict(kind="dense", ff=56)),
+            dict(type="general_delta", mixer=_delta(3, 20, 5), mlp=_scored_experts(24, 6, 2, 2.5, (3, 2), 40)),
+            dict(type="attention", mixer=_masked(4, 2, 24, 10, 0.25, 24, 50.0, 70, conv=3), mlp=None),
+            dict(type="attention", mixer=_masked(2, 2, 10, 10, 0.4, 4, 1000.0, 1, conv=1), mlp=_scored_experts(16, 4, 4)),
+            dict(type="general_delta", mixer=_delta(1, 36, 3), mlp=None),
+        ]), seed=51, std=0.12),
+    "T2": dict(
+        config=dict(architecture="Tarupel", vocab=512, width=256, norm=dict(eps=2e-5), embedding=dict(scale=8.0),
+                    residual_mult=0.5, loop=dict(start=0, stop=2, times=2), layers=[
+            dict(type="attention", mixer=_masked(4, 2, 64, 64, 0.11, 32, 10000.0, 64, conv=4),
+                 mlp=_scored_experts(64, 12, 4, 1.5, (4, 3), 96)),
+            dict(type="general_delta", mixer=_delta(4, 64, 16), mlp=dict(kind="dense", ff=384)),
+            dict(type="attention_2", mixer=_masked(2, 1, 128, 128, 0.09, 64, 500000.0, 100), mlp=_scored_experts(128, 6, 1, 0.5, (2, 1))),
+            dict(type="attention_2", mixer=_masked(8, 8, 32, 32, 0.2, 32, 10000.0, 64), mlp=None),
+        ]), seed=52, std=0.06),
+    "T3": dict(
+        config=dict(architecture="Tarupel", vocab=300, width=64, norm=dict(eps=1e-5), layers=[
+            dict(type="attention", mixer=_masked(2, 1, 16, 24, 0.3, 8, 30.0, 33, conv=5), mlp=None),
+            dict(type="attention_2", mixer=_masked(2, 2, 8, 8, 0.35, 2, 30.0, 1), mlp=dict(kind="dense", ff=40)),
+            dict(type="general_delta", mixer=_delta(2, 16, 4), mlp=_scored_experts(32, 3, 2, shared=24)),
+        ]), seed=53, std=0.15),
+}
+
+STEADY_CHANNEL = 0  # the channel a steadily routed Tarupel folder keeps constant
+
+
+def make_tarupel_dir(path, name, dtype=torch.bfloat16, edit=None, steady_routing=False):
+    """A model folder of a tiny Tarupel configuration (a name of TARUPEL, or a spec of the caller's
+    own) with seeded random weights; `edit` (a function of the name -> tensor dict) may change them
+    before they are written. Norm weights (single numbers) and the read-out norm's are N(1, 0.2),
+    layer scales N(1, 0.3), the shift's mix uniform in [0, 1], biases and the other vectors N(0, 0.5),
+    the decay's bias N(0, 2): some channels forget within a few tokens, others carry far.
+    The choice of experts is a step function of the router's input: with random weights a
+    runner-up now and then comes within a rounding of bfloat16 activations of the last chosen
+    expert, and the engine and the float64 implementation then choose differently.
+    `steady_routing` is for comparisons in bfloat16: one channel of the stream is the same large
+    number for every token (the embedding puts it there, no sublayer adds to it) and the routers
+    weigh it by 0, 0.5, 1, ... per expert and everything else a fifth as much, so the same experts win for every token (their weights, the
+    scores, still depend on the token) and no comparison rests on a close call."""
+    from llama_rs_metal_b200.engine.model import DecoderModel
+    from llama_rs_metal_b200.registry import find_architecture
+    from llama_rs_metal_b200.runtime import Runtime
+    from llama_rs_metal_b200.weights.random_init import _generator, random_tensors, write_model_folder
+    spec = TARUPEL[name] if isinstance(name, str) else name
+    arch = find_architecture(spec["config"])
+    config = arch.config_class.from_dict(spec["config"])
+    model = DecoderModel(arch.plan(config), Runtime(torch.device("cpu"), torch.float32))
+    tensors = random_tensors(model.tensor_specs(), spec["seed"], std=spec["std"], vector_mean=0.0, vector_std=0.5,
+                             dtype=dtype)
+    scale = config.embedding_scale
+    for name_, t in tensors.items():
+        last = name_.rsplit(".", 1)[-1]
+        if last in ("norm", "norm1", "norm2"):
+            t.mul_(0.4).add_(1.0)
+        elif last in ("ls1", "ls2"):
+            t.mul_(0.6).add_(1.0)
+            if steady_routing:
+                t[STEADY_CHANNEL] = 0.0
+        elif last == "shift":
+            t.copy_(torch.rand(t.shape, generator=_generator(spec["seed"], name_), dtype=torch.float32))
+        elif last == "w0":
+            t.mul_(4.0)
+        elif steady_routing and name_ == "embed":
+            t[:, STEADY_CHANNEL] = 4.0 * spec["std"] * 4.0   # several times a typical entry, before the scale
+        elif steady_routing and name_ == "loop.step":
+            t[:, STEADY_CHANNEL] = 0.0
+        elif steady_routing and last == "router":
+            t.mul_(0.2)
+            t[:, STEADY_CHANNEL] = 0.5 * torch.arange(t.shape[0])
+    if edit is not None:
+        edit(tensors)
+    return write_model_folder(path, config.to_dict(), tensors, spec["seed"])
+
+
 def random_tokens(seed, length, vocab):
     rng = np.random.default_rng(seed)
     return [int(t) for t in rng.integers(0, vocab, size=length)]
