@@ -46,7 +46,7 @@ def _sample_args(parser: argparse.ArgumentParser) -> None:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    parser = argparse.ArgumentParser(prog="llama-cli", description="B200 inference for the registered decoders (Llama 3 dense, Kikalix, Pibuvik, Norevik)")
+    parser = argparse.ArgumentParser(prog="llama-cli", description="B200 inference for the registered decoders (Llama 3 dense, Kikalix, Pibuvik, Norevik, Tarupel)")
     commands = parser.add_subparsers(dest="command", required=True)
     inspect = commands.add_parser("inspect", help="Inspect a model folder without initializing the GPU")
     inspect.add_argument("model")

@@ -168,3 +168,38 @@ def test_generate_runs_the_fourth_architecture(tmp_path):
     sampled = [subprocess.run([sys.executable, CLI, "generate", "-m", folder, "-p", "4,5", "-n", "6", "--seed", "11"],
                               capture_output=True, text=True).stdout for _ in range(2)]
     assert sampled[0] == sampled[1] and sampled[0].count("\t") == 6
+
+
+def test_inspect_and_random_take_the_fifth_architecture(tmp_path):
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(helpers.TARUPEL["T3"]["config"]))
+    out = subprocess.run([sys.executable, CLI, "random", "--config", str(config), "--out", str(tmp_path / "m"),
+                          "--seed", "3", "--std", "0.1", "--norm-mean", "1", "--norm-std", "0.1"],
+                         capture_output=True, text=True, env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert out.returncode == 0, out.stderr
+    out = subprocess.run([sys.executable, CLI, "inspect", str(tmp_path / "m"), "--tensors"],
+                         capture_output=True, text=True, env={**os.environ, "CUDA_VISIBLE_DEVICES": ""})
+    assert out.returncode == 0, out.stderr
+    report = json.loads(out.stdout)
+    assert report["config"]["architecture"] == "Tarupel" and len(report["config"]["layers"]) == 3
+    assert report["tensors"]["l0.norm1"]["dimensions"] == [] and report["tensors"]["l0.shift"]["dimensions"] == [64]
+    assert report["tensors"]["l0.mix.q.conv"]["dimensions"] == [32, 5]
+    assert report["tensors"]["l1.mix.k.norm"]["dimensions"] == [16]
+    assert report["tensors"]["l2.mix.w1"]["dimensions"] == [4, 64]
+    assert report["tensors"]["l2.mlp.shared.sg"]["dimensions"] == [1, 64]
+    assert "l0.norm2" not in report["tensors"] and "loop.step" not in report["tensors"]
+
+
+@pytest.mark.gpu
+def test_generate_runs_the_fifth_architecture(tmp_path):
+    folder = helpers.make_tarupel_dir(str(tmp_path / "m"), "T1")
+    for flags in (["--float-weights-f32"], []):
+        out = subprocess.run([sys.executable, CLI, "generate", "-m", folder, "-p", "1,2,3", "-p", "9", "-n", "5",
+                              "--temperature", "0", "-c", "64", *flags], capture_output=True, text=True)
+        assert out.returncode == 0, out.stderr
+        finished = [json.loads(l) for l in out.stdout.strip().splitlines() if l.startswith("{")]
+        assert len(finished) == 2 and all(f["reason"] == "length" and f["tokens"] == 5 for f in finished)
+        assert "Tarupel" in out.stderr
+    sampled = [subprocess.run([sys.executable, CLI, "generate", "-m", folder, "-p", "4,5", "-n", "6", "--seed", "11"],
+                              capture_output=True, text=True).stdout for _ in range(2)]
+    assert sampled[0] == sampled[1] and sampled[0].count("\t") == 6
