@@ -79,6 +79,8 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
 
   const int kt_first = first_visible_key(q0, window) / kTile;
   const int kt_last = qt;
+  // the first key each of this thread's two rows sees (found once: a chunk's start costs a division)
+  const int row_first[2] = {first_visible_key(row0 + g, window), first_visible_key(row0 + g + 8, window)};
   const size_t kv_pitch = static_cast<size_t>(kv_heads) * D;
   auto issue = [&](int kt, int stage) {
     const size_t base = (static_cast<size_t>(start + kt * kTile) * kv_heads + kh) * D;
@@ -108,7 +110,7 @@ __global__ __launch_bounds__(kThreads) void attention_prefill_tiled_kernel(
       for (int e = 0; e < 4; ++e) {
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = row0 + g + 8 * (e >> 1);
-        const bool visible = key <= query && key >= first_visible_key(query, window);
+        const bool visible = key <= query && key >= row_first[e >> 1];
         s[nt][e] = visible ? s[nt][e] * scale_row[e >> 1] - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }
@@ -180,6 +182,8 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
   // keys the tile's queries see: from the first query's window to the last query's own position
   const int first_key = first_visible_key(before + q0, window);
   const int kt_first = first_key / kTile;
+  const int row_first[2] = {first_visible_key(before + row0 + g, window),
+                            first_visible_key(before + row0 + g + 8, window)};
   const int kt_last = (before + min(q0 + kTile, n) - 1) / kTile;
   auto issue = [&](int kt, int stage) {
     const int page = table[kt];
@@ -213,7 +217,7 @@ __global__ __launch_bounds__(kThreads) void attention_extend_tiled_kernel(
       for (int e = 0; e < 4; ++e) {
         const int key = kt * kTile + 8 * nt + 2 * t + (e & 1);
         const int query = before + row0 + g + 8 * (e >> 1);  // position in the sequence
-        const bool visible = key <= query && key >= first_visible_key(query, window);
+        const bool visible = key <= query && key >= row_first[e >> 1];
         s[nt][e] = visible ? s[nt][e] * scale_row[e >> 1] - slope_log2 * static_cast<float>(query - key) : -INFINITY;
       }
     }

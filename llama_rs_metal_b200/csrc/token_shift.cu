@@ -61,10 +61,13 @@ __global__ void scaled_add_kernel(float* x, const float* y, const float* __restr
   if (idx < n) x[idx] = fmaf(factor[idx % width], y[idx], x[idx]);
 }
 
-// y[t, :] *= sigmoid(x[t, :] . w): one gate per token from its input row (float32 sum), on a
-// float32 output row. One CTA per token.
+// y[t, :] = sigmoid(x[t, :] . w) * y[t, :] + planes[0][t, :] + planes[1][t, :] + ...: one gate per
+// token from its input row (float32 sum) on a float32 output row, and `count` planes [tokens,
+// out_width] of float32 sums that belong beside it, added in plane order. gridDim.y CTAs per token
+// share its columns (each forms the gate itself), so that few tokens still fill the device.
 template <typename A>
-__global__ void row_gate_kernel(float* y, const A* x, const float* __restrict__ w, int in_width, int out_width) {
+__global__ void row_gate_kernel(float* y, const A* x, const float* __restrict__ w, int in_width, int out_width,
+                                const float* planes, int count, size_t plane) {
   __shared__ float scratch[32];
   pdl_trigger();
   pdl_wait();
@@ -74,7 +77,12 @@ __global__ void row_gate_kernel(float* y, const A* x, const float* __restrict__ 
     acc = fmaf(to_f32(x[static_cast<size_t>(t) * in_width + c]), w[c], acc);
   const float z = block_sum(acc, scratch);
   const float gate = 1.0f / (1.0f + expf(-z));
-  for (int c = threadIdx.x; c < out_width; c += blockDim.x) y[static_cast<size_t>(t) * out_width + c] *= gate;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < out_width; c += gridDim.y * blockDim.x) {
+    const size_t at = static_cast<size_t>(t) * out_width + c;
+    float v = y[at] * gate;
+    for (int p = 0; p < count; ++p) v += planes[p * plane + at];
+    y[at] = v;
+  }
 }
 
 }  // namespace
@@ -130,15 +138,24 @@ LRM_API int lrm_scaled_add_norm(float* x, const float* y, const float* factor, c
   return 0;
 }
 
+// planes: float32 [count, tokens, out_width] or null (count 0).
 LRM_API int lrm_row_gate(float* y, const void* x, int x_dtype, const float* w, int tokens, int in_width, int out_width,
-                         cudaStream_t stream) {
+                         const float* planes, int count, cudaStream_t stream) {
   if (tokens <= 0) return 0;
-  if (y == nullptr || w == nullptr || in_width <= 0 || out_width <= 0) return LRM_BAD_ARGUMENT;
+  if (y == nullptr || w == nullptr || in_width <= 0 || out_width <= 0 || count < 0 || (count > 0 && planes == nullptr))
+    return LRM_BAD_ARGUMENT;
+  const size_t plane = static_cast<size_t>(tokens) * out_width;
+  // about four CTAs per SM in all, a CTA per 256 columns at most
+  int tiles = (592 + tokens - 1) / tokens;
+  if (tiles > (out_width + 255) / 256) tiles = (out_width + 255) / 256;
+  if (tiles < 1) tiles = 1;
+  const dim3 grid(tokens, tiles);
   if (x_dtype == LRM_F32)
-    LRM_LAUNCH(row_gate_kernel<float>, tokens, 256, 0, stream, y, static_cast<const float*>(x), w, in_width, out_width);
+    LRM_LAUNCH(row_gate_kernel<float>, grid, 256, 0, stream, y, static_cast<const float*>(x), w, in_width, out_width,
+               planes, count, plane);
   else if (x_dtype == LRM_BF16)
-    LRM_LAUNCH(row_gate_kernel<__nv_bfloat16>, tokens, 256, 0, stream, y, static_cast<const __nv_bfloat16*>(x), w,
-               in_width, out_width);
+    LRM_LAUNCH(row_gate_kernel<__nv_bfloat16>, grid, 256, 0, stream, y, static_cast<const __nv_bfloat16*>(x), w,
+               in_width, out_width, planes, count, plane);
   else
     return LRM_BAD_ARGUMENT;
   return 0;

@@ -392,15 +392,23 @@ def scaled_add_norm_(x: torch.Tensor, y: torch.Tensor, factor: torch.Tensor, wei
     return out
 
 
-def row_gate_(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """y[t, :] *= sigmoid(x[t, :] . weight): y float32 [T, N], x [T, W], weight float32 [W]."""
+def row_gate_(y: torch.Tensor, x: torch.Tensor, weight: torch.Tensor,
+              planes: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """y[t, :] = sigmoid(x[t, :] . weight) * y[t, :] (+ planes[0][t, :] + planes[1][t, :] + ..., in that
+    order): y float32 [T, N], x [T, W], weight float32 [W], planes float32 [n, T, N]."""
     _check(y, "y", torch.float32, 2)
     _check(x, "x", dims=2)
     _check(weight, "weight", torch.float32, 1)
     if x.shape[0] != y.shape[0] or weight.numel() != x.shape[1]:
         raise InvalidError("row_gate_: shapes do not agree")
+    count = 0
+    if planes is not None and planes.shape[0]:
+        _check(planes, "planes", torch.float32, 3)
+        if tuple(planes.shape[1:]) != tuple(y.shape):
+            raise InvalidError("row_gate_: planes must be [n, T, N]")
+        count = planes.shape[0]
     _done(_lib().lrm_row_gate(_ptr(y), _ptr(x), _code(x.dtype), _ptr(weight), y.shape[0], x.shape[1], y.shape[1],
-                              _stream()), "row_gate_")
+                              _ptr(planes if count else None), count, _stream()), "row_gate_")
     return y
 
 

@@ -158,7 +158,8 @@ WORK: Dict[str, Callable[..., Tuple[float, float]]] = {
         2.0 * _v(a[25]) * (_v(a[26]) * _v(a[28]) + _v(a[27]) * (_v(a[28]) + _v(a[29]))) * max(1, _v(a[4]))),
     "lrm_token_shift": lambda a: (_v(a[8]) * _v(a[9]) * 2.0 * _ELEM[_v(a[1])], 0),
     "lrm_scaled_add": lambda a: (12.0 * _v(a[3]) * _v(a[4]), 0),
-    "lrm_row_gate": lambda a: (_v(a[4]) * (_v(a[5]) * _ELEM[_v(a[2])] + 8.0 * _v(a[6])), 0),
+    "lrm_row_gate": lambda a: (_v(a[4]) * (_v(a[5]) * _ELEM[_v(a[2])] + (8.0 + 4.0 * _v(a[8])) * _v(a[6])), 0),
+    "lrm_scaled_add_norm": lambda a: (_v(a[8]) * _v(a[9]) * (12.0 + _ELEM[_v(a[7])]), 5.0 * _v(a[8]) * _v(a[9])),
     "lrm_gelu_tanh_mul": lambda a: (_v(a[4]) * _v(a[5]) * (2.0 * _ELEM[_v(a[1])] + _ELEM[_v(a[3])]), 0),
     "lrm_tanh_columns": lambda a: (_v(a[5]) * _v(a[6]) * (_ELEM[_v(a[1])] + _ELEM[_v(a[4])]), 0),
 }

@@ -144,6 +144,10 @@ class MixtureOfExperts(FeedForward):
             # a block that puts a norm between this part and the stream: the shared part's float32
             # output (or the all-experts product's) is what everything else is added to
             out = self.shared.forward(x, ctx, residual=None) if self.shared is not None else None
+            if self.shared_gate and not dense:
+                # the gate on the shared part and the experts' planes beside it in one pass
+                planes = ops.moe_experts_rows(x, self.gate_up, self.down, ids, weights, self.limit, self.alpha, self.act, x32)
+                return ops.row_gate_(out, x, self.shared_gate_weight, planes)
             if self.shared_gate:
                 ops.row_gate_(out, x, self.shared_gate_weight)
             if dense:
