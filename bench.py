@@ -277,17 +277,17 @@ def tarupel_shape(width, heads, kv_heads, ff, experts, top, window, layers, voca
     """A Tarupel configuration with layers of a real model's widths: a generalized delta rule (heads
     of 64), chunked attention with short convolutions (head size 128, a quarter of it rotated, chunks
     of `window`) and windowed attention with row norms (head size 128) in turn; behind each a mixture
-    of `experts` experts in four groups of which three are kept, `top` chosen, and a gated shared
+    of `experts` experts in four groups of which two are kept, `top` chosen, and a gated shared
     expert as wide as one expert. The first two layers loop twice."""
     d = 128
     moe = dict(kind="moe", expert=dict(ff=ff), shared=dict(ff=ff),
-               router=dict(experts=experts, top=top, scale=1.5, groups=dict(count=4, keep=3)))
+               router=dict(experts=experts, top=top, scale=2.0, groups=dict(count=4, keep=2)))
     kinds = [
         dict(type="general_delta", mixer=dict(heads=width // 64, dim=64, decay_rank=64), mlp=moe),
         dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=d, vdim=d, scale=d ** -0.5, conv=4,
-                                          rot=dict(dims=32, base=50000.0), mask=dict(size=window)), mlp=moe),
+                                          rot=dict(dims=32, base=10000.0), mask=dict(size=window)), mlp=moe),
         dict(type="attention_2", mixer=dict(heads=heads, kv_heads=kv_heads, dim=d, vdim=d, scale=d ** -0.5,
-                                            rot=dict(dims=32, base=1000000.0), mask=dict(size=window)), mlp=moe),
+                                            rot=dict(dims=64, base=500000.0), mask=dict(size=window)), mlp=moe),
     ]
     return dict(architecture="Tarupel", vocab=vocab, width=width, norm=dict(eps=1e-5), embedding=dict(scale=1.0),
                 residual_mult=0.5, layers=[dict(kinds[i % 3]) for i in range(layers)], loop=dict(start=0, stop=2, times=2))

@@ -2,7 +2,7 @@
 // keys on the way: one CTA per token takes the projection row [q_heads * d | kv_heads * d |
 // kv_heads * dv] through, in this order and each only if asked for,
 //   1. the projections' biases (float32 [row]);
-//   2. a short causal convolution over time per channel (taps [row, n], the last tap the current
+//   2. a short causal convolution over time per channel (taps [n, row], the last row the current
 //      token's, no bias, zeros before the sequence's start); inputs before the step's first token
 //      come from the sequence's tail [n - 1, row] of unbiased projections in the state storage,
 //      the bias added here where the input's position is not before the start;
@@ -56,20 +56,37 @@ __global__ void shaped_qkv_kernel(const S* proj, const float* __restrict__ bias,
   } else {
     const int b = seq_of_token[t], local = t - cu_seqlens[b], slot = slots[b];
     const float* tail = slot >= 0 ? tails + static_cast<size_t>(slot) * (n - 1) * width : nullptr;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-      const float add = bias != nullptr ? bias[c] : 0.f;
-      float acc = 0.f;
+    // a thread takes kGroup columns at a time, so that the loads of one input row are all under way
+    // before the first is used (one column after another, a CTA waited for n loads in turn per column)
+    constexpr int kGroup = 8;
+    for (int first = 0; first < width; first += kGroup * blockDim.x) {
+      float acc[kGroup], add[kGroup];
+#pragma unroll
+      for (int e = 0; e < kGroup; ++e) {
+        const int c = first + e * blockDim.x + threadIdx.x;
+        acc[e] = 0.f;
+        add[e] = (bias != nullptr && c < width) ? bias[c] : 0.f;
+      }
       for (int back = n - 1; back >= 0; --back) {  // oldest input first
         if (pos - back < 0) continue;              // before the sequence's start: zero
         const int at = local - back;
-        float x;
-        if (at >= 0)
-          x = to_f32(proj[static_cast<size_t>(t - back) * width + c]);
-        else
-          x = tail != nullptr ? tail[static_cast<size_t>(n - 1 + at) * width + c] : 0.f;
-        acc = fmaf(taps[static_cast<size_t>(c) * n + (n - 1 - back)], x + add, acc);
+        const S* from_step = at >= 0 ? proj + static_cast<size_t>(t - back) * width : nullptr;
+        const float* from_tail = (at < 0 && tail != nullptr) ? tail + static_cast<size_t>(n - 1 + at) * width : nullptr;
+        const float* tap = taps + static_cast<size_t>(n - 1 - back) * width;
+#pragma unroll
+        for (int e = 0; e < kGroup; ++e) {
+          const int c = first + e * blockDim.x + threadIdx.x;
+          if (c < width) {
+            const float x = from_step != nullptr ? to_f32(from_step[c]) : from_tail != nullptr ? from_tail[c] : 0.f;
+            acc[e] = fmaf(tap[c], x + add[e], acc[e]);
+          }
+        }
       }
-      row[c] = acc;
+#pragma unroll
+      for (int e = 0; e < kGroup; ++e) {
+        const int c = first + e * blockDim.x + threadIdx.x;
+        if (c < width) row[c] = acc[e];
+      }
     }
   }
   __syncthreads();
@@ -131,7 +148,7 @@ __global__ void shaped_qkv_kernel(const S* proj, const float* __restrict__ bias,
 }  // namespace
 
 // proj: [tokens, q_heads * d + kv_heads * (d + dv)] float32 or bfloat16 (in_dtype); outputs of
-// out_dtype. bias, taps (+ tails, cu_seqlens, seq_of_token, slots), q_norm + k_norm, inv_freq
+// out_dtype. bias, taps (float32 [n, row]; + tails, cu_seqlens, seq_of_token, slots), q_norm + k_norm, inv_freq
 // (double [rotary / 2]) may each be null: that step is then left out. kv_heads 0: queries only.
 LRM_API int lrm_shaped_qkv_store(const void* proj, int in_dtype, const float* bias, const float* taps, int n,
                                  const float* tails, const int* cu_seqlens, const int* seq_of_token,
@@ -162,7 +179,7 @@ LRM_API int lrm_shaped_qkv_store(const void* proj, int in_dtype, const float* bi
       if (e != cudaSuccess) return static_cast<int>(e);                                                         \
       raised = true;                                                                                            \
     }                                                                                                           \
-    LRM_LAUNCH((shaped_qkv_kernel<ST, AT>), tokens, 256, bytes, stream, static_cast<const ST*>(proj), bias, taps, n, \
+    LRM_LAUNCH((shaped_qkv_kernel<ST, AT>), tokens, width >= 2048 ? 512 : 256, bytes, stream, static_cast<const ST*>(proj), bias, taps, n, \
                tails, cu_seqlens, seq_of_token, slots, positions, q_norm, k_norm, row_eps, inv_freq, rotary,    \
                pairing, head_norm, head_eps, static_cast<AT*>(q_out), static_cast<AT*>(k_out),                  \
                static_cast<AT*>(v_out), static_cast<AT*>(k_pages), static_cast<AT*>(v_pages), dest_rows, q_heads, \

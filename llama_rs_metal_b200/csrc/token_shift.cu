@@ -92,7 +92,9 @@ LRM_API int lrm_token_shift(const void* h, int dtype, const float* mix, float* l
                             cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (width <= 0 || mix == nullptr || last == nullptr) return LRM_BAD_ARGUMENT;
-  const int threads = width >= 256 ? 256 : ((width + 31) / 32) * 32;
+  // about four columns per thread: a row's loads are under way together
+  int threads = ((width / 4 + 31) / 32) * 32;
+  threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
   if (dtype == LRM_F32)
     LRM_LAUNCH(token_shift_kernel<float>, tokens, threads, 0, stream, static_cast<const float*>(h), mix, last,
                static_cast<float*>(out), cu_seqlens, seq_of_token, slots, width);
@@ -120,7 +122,8 @@ LRM_API int lrm_scaled_add_norm(float* x, const float* y, const float* factor, c
   if (x == nullptr || y == nullptr || factor == nullptr || w == nullptr || out == nullptr || width <= 0)
     return LRM_BAD_ARGUMENT;
   const unsigned grid = static_cast<unsigned>(rows);
-  const int threads = width >= 1024 ? 256 : width >= 256 ? 128 : 64;
+  int threads = ((width / 4 + 31) / 32) * 32;  // about four columns per thread
+  threads = threads < 64 ? 64 : threads > 1024 ? 1024 : threads;
 #define LRM_SAN(WT, OT)                                                                                          \
   LRM_LAUNCH((scaled_add_norm_kernel<WT, OT>), grid, threads, 0, stream, x, y, factor, static_cast<const WT*>(w), eps, \
              static_cast<OT*>(out), width)

@@ -67,7 +67,7 @@ class Shaping:
     """What some attention layers do to their queries and keys between the projection and the
     attention itself (csrc/shaped_qkv.cu applies it in this order, each step only if given).
 
-    taps: float32 [projection row, n], a causal convolution over time on every projected channel,
+    taps: float32 [n, projection row], a causal convolution over time on every projected channel,
         with `tails`, the StateView of the sequences' last n - 1 unbiased projections.
     row_norm: (q weight, k weight), an RMS norm over all query columns and one over all key columns
         (eps `row_eps`).

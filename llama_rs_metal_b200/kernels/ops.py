@@ -559,7 +559,8 @@ def shaped_qkv_store(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: i
                      keep_packed: bool = True):
     """Split a fused [T, Hq*d + Hk*d + Hk*dv] projection (float32, or `out_dtype`) whose queries and
     keys are shaped on the way, each step only if asked for and in this order: `bias` (float32
-    [row]); a causal convolution per channel (`taps` float32 [row, n] with the sequences' `tails`
+    [row]); a causal convolution per channel (`taps` float32 [n, row], the last row the current
+    token's, with the sequences' `tails`
     float32 [slots, n - 1, row] of unbiased projections, rewritten afterwards); an RMS norm over all
     query columns and one over all key columns (`row_norm` = (q weight, k weight), `row_eps`); the
     rotation of each head's first `rotary` dimensions by `inv_freq` (float64 [rotary/2]; split halves,
@@ -578,9 +579,9 @@ def shaped_qkv_store(qkv: torch.Tensor, q_heads: int, kv_heads: int, head_dim: i
     n = 0
     if taps is not None:
         _check(taps, "taps", torch.float32, 2)
-        n = taps.shape[1]
-        if taps.shape[0] != width:
-            raise InvalidError("shaped_qkv_store: one row of taps per projected column")
+        n = taps.shape[0]
+        if taps.shape[1] != width:
+            raise InvalidError("shaped_qkv_store: one tap per projected column in every row of taps")
         if n > 1:
             _check(tails, "tails", torch.float32, 3)
             if tuple(tails.shape[1:]) != (n - 1, width):

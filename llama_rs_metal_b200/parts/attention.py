@@ -144,7 +144,8 @@ class Attention(Mixer):
             self.position.bind({n[len("position."):]: t for n, t in weights.items()
                                 if n.startswith("position.")}, runtime)
         if self.conv_taps:
-            self.taps = torch.cat([weights[n + "_conv.weight"] for n in "qkv"], dim=0).to(torch.float32).contiguous()
+            # [taps, projection row]: the kernel reads one tap of many channels at a time
+            self.taps = torch.cat([weights[n + "_conv.weight"] for n in "qkv"], dim=0).to(torch.float32).t().contiguous()
         if self.row_norm_eps is not None:
             self.row_norm = (weights["q_norm.weight"].to(torch.float32).contiguous(),
                              weights["k_norm.weight"].to(torch.float32).contiguous())

@@ -345,11 +345,11 @@ TARUPEL = {
             dict(type="general_delta", mixer=_delta(1, 36, 3), mlp=None),
         ]), seed=51, std=0.12),
     "T2": dict(
-        config=dict(architecture="Tarupel", vocab=512, width=256, norm=dict(eps=2e-5), embedding=dict(scale=8.0),
-                    residual_mult=0.5, loop=dict(start=0, stop=2, times=2), layers=[
-            dict(type="attention", mixer=_masked(4, 2, 64, 64, 0.11, 32, 10000.0, 64, conv=4),
-                 mlp=_scored_experts(64, 12, 4, 1.5, (4, 3), 96)),
-            dict(type="general_delta", mixer=_delta(4, 64, 16), mlp=dict(kind="dense", ff=384)),
+        config=dict(architecture="Tarupel", vocab=512, width=192, norm=dict(eps=2e-5), embedding=dict(scale=8.0),
+                    residual_mult=0.8, loop=dict(start=0, stop=2, times=2), layers=[
+            dict(type="attention", mixer=_masked(4, 2, 64, 64, 0.11, 32, 10000.0, 64, conv=2),
+                 mlp=_scored_experts(80, 12, 3, 2.0, (4, 2), 112)),
+            dict(type="general_delta", mixer=_delta(3, 64, 8), mlp=dict(kind="dense", ff=448)),
             dict(type="attention_2", mixer=_masked(2, 1, 128, 128, 0.09, 64, 500000.0, 100), mlp=_scored_experts(128, 6, 1, 0.5, (2, 1))),
             dict(type="attention_2", mixer=_masked(8, 8, 32, 32, 0.2, 32, 10000.0, 64), mlp=None),
         ]), seed=52, std=0.06),

@@ -488,7 +488,8 @@ def test_shaped_split_in_portions_matches_the_definition(taps_n, row_norm, rot, 
         got, at = [], 0
         for n in cuts:
             part = proj[at:at + n].to(DEV).contiguous()
-            args = dict(bias=dev(bias), taps=dev(taps), tails=tails if taps_n > 1 else None,
+            args = dict(bias=dev(bias), taps=None if taps is None else taps.t().contiguous().to(DEV),
+                        tails=tails if taps_n > 1 else None,
                         cu_seqlens=torch.tensor([0, n], dtype=torch.int32, device=DEV),
                         seq_of_token=torch.zeros(n, dtype=torch.int32, device=DEV),
                         slots=torch.tensor([1], dtype=torch.int32, device=DEV),
