@@ -219,9 +219,9 @@ int launch_scan(const float* q, const float* k, const float* v, const float* g, 
 // registers a thread can keep bound ROWS to 64).
 int g_scan_rows = 16;  // most rows a thread holds (tuning: lrm_linear_state_scan_rows)
 
-void scan_shape(int d, int* rows, int* parts) {
+void scan_shape(int d, int* rows, int* parts, int most_rows) {
   int P = 1;
-  while (P < 32 && (d + P - 1) / P > g_scan_rows) P <<= 1;
+  while (P < 32 && (d + P - 1) / P > most_rows) P <<= 1;
   int need = (d + P - 1) / P, R = 4;
   while (R < need) R <<= 1;
   *rows = R;
@@ -233,7 +233,15 @@ int dispatch_scan(const float* q, const float* k, const float* v, const float* g
                   const float* beta, const float* look, const float* put, float* state, float* out, const int* cu_seqlens, const int* slots,
                   int seqs, int H, int KH, int d, int dv, cudaStream_t stream) {
   int R, P;
-  scan_shape(d, &R, &P);
+  scan_shape(d, &R, &P, g_scan_rows);
+  if (MODE == 3 && g_scan_rows > 8) {
+    // Few sequences (one prompt) leave most SMs without a CTA, and every CTA walks its tokens one
+    // after another: with half the rows per thread a head's columns go to twice as many CTAs and a
+    // token's chain of sums is shorter (one prompt of 2,048 tokens, 32 heads of 64 x 64: 643 against
+    // 792 us; a quarter of the rows: 861). Steps that fill the device keep the standard shape.
+    const long long ctas = static_cast<long long>((dv + kScanThreads / P - 1) / (kScanThreads / P)) * H * seqs;
+    if (ctas < 148) scan_shape(d, &R, &P, g_scan_rows / 2);
+  }
 #define LRM_SCAN_CASE(N)                                                                             \
   case N:                                                                                            \
     return launch_scan<N, MODE>(q, k, v, g, head_decay, beta, look, put, state, out, cu_seqlens, slots, seqs, H, \
