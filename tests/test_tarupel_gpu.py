@@ -366,6 +366,27 @@ def test_configurations_drawn_at_random(engine, tmp_path, seed):
         runner.check_device_status()
 
 
+@pytest.mark.parametrize("experts,top,groups,shared", [(24, 3, (6, 2), 40), (20, 5, None, None), (32, 2, (4, 4), 16)])
+def test_many_experts_take_the_logits_first_router(engine, tmp_path, experts, top, groups, shared):
+    """More router outputs than a token's CTA scores itself and a prompt of 300 tokens: the logits come
+    from the float32 product and the scored choice is made from them; then decoding (the one-launch
+    router) from the same state."""
+    layer = dict(type="attention_2", mixer=helpers._masked(2, 1, 16, 16, 0.25, 8, 100.0, 50),
+                 mlp=helpers._scored_experts(24, experts, top, 1.7, groups, shared))
+    spec = dict(config=dict(architecture="Tarupel", vocab=128, width=48, norm=dict(eps=1e-5), residual_mult=0.9,
+                            layers=[layer, dict(layer, type="general_delta", mixer=helpers._delta(2, 8, 3))]),
+                seed=77 + experts, std=0.15)
+    folder = helpers.make_tarupel_dir(str(tmp_path / "m"), spec)
+    config, tensors = P.read_model(folder)
+    tokens = helpers.random_tokens(experts, 330, 128)
+    ref = P.forward(config, tensors, tokens).numpy()
+    runner, cache, _ = open_runner(engine, folder, "float32")
+    slot = cache.open_slot()
+    rows = [runner.step([entry(slot, tokens[:300])]).cpu().numpy()]
+    rows += [runner.step([entry(slot, [t])]).cpu().numpy() for t in tokens[300:]]
+    close(np.concatenate(rows), ref, "float32", f"{experts} experts")
+
+
 # --------------------------------------------------------------------------- the generalized delta rule
 def plain_general_scan(r, k, v, g, look, put, state):
     """One sequence, float64: everything [T, H, d] but v [T, H, dv]; state [H, d, dv], updated in place."""
